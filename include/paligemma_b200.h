@@ -282,7 +282,24 @@ int pg_prefetch_l2(const void* ptr, long long bytes, int ctas, int evict_last, v
 int pg_gemm_simt(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, int tokens, int features,
                  int K, int in_f32, int out_f32, void* stream);
 
-/* out[t, 0:D] (fp32) = table[tokens[t], col0 : col0 + D] * scale  (embedding lookup; table bf16 or fp32, pitch ld). */
+/* pg_layernorm_shift: rows of x (fp32 [rows, D]) through one or two layer norms that share the row's mean and variance:
+ *   a = (x - mean) / sqrt(var + eps) * w1 + b1 -> out1, the same with (w2, b2) -> out2 (out2 NULL: one norm).
+ * shift != NULL (fp32 [D]): out1[t] = a[t] + (a[t-1] - a[t]) * shift, where a[t-1] belongs to the previous token of the SAME
+ * sequence: zeros at position 0, the row before inside an entry, and for an entry's first row the fp32 state slot
+ * state[entry_slot[e], 0:D], which afterwards holds a of the entry's last row.  out1 / out2: bf16, or fp32 when out_f32.
+ * pg_glu: out[t, f] from gu[t, f] (gate) and gu[t, F + f] (up): kind 1 silu(g) * u; kind 2 g' = min(g, limit),
+ *   u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1). */
+int pg_layernorm_shift(const float* x, const float* w1, const float* b1, const float* shift, const float* w2, const float* b2, void* out1,
+                       void* out2, float* state, const int* pos, const int* row_entry, const int* entry_row0, const int* entry_n,
+                       const int* entry_slot, int rows, int D, float eps, int out_f32, void* stream);
+int pg_glu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int kind, float limit, float alpha, int act_f32,
+           void* stream);
+
+/* The same product with out[t, f] = sum + bias[f] (bias fp32 [features] or NULL) + (accumulate != 0 ? out[t, f] : 0): projections
+ * with biases and projections that add into the fp32 residual stream. */
+int pg_gemm_simt_bias(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, const float* bias,
+                      int accumulate, int tokens, int features, int K, int in_f32, int out_f32, void* stream);
+
 /* grid.z = batch independent products out_b = x_b w_b^T; operand b starts batch_* elements after operand b - 1 (per-head
  * projections: x a column slice per head, w one matrix per head). */
 int pg_gemm_simt_batched(const void* x, long long ldx, long long batch_x, const void* w, long long ldw, long long batch_w, void* out,
@@ -318,10 +335,29 @@ int pg_side_gate(const float* z, long long ldz, const int* tokens, const void* t
  * q and k heads are RMS-normalised over dim with the shared weights q_norm / k_norm, then the first rot_dims dimensions are
  * rotated in interleaved pairs (2i, 2i+1) by pos[t] * freq[i] (freq: double [rot_dims / 2]); v heads are divided by their
  * root mean square over vdim.  q goes to q_out [rows, H * dim]; k and v go to cache row
- * page_table[row_entry[t] * max_pages + pos[t] / page] * page + pos[t] % page of k_pages [.., G * dim] / v_pages [.., G * vdim]. */
+ * page_table[row_entry[t] * max_pages + pos[t] / page] * page + pos[t] % page of k_pages [.., G * dim] / v_pages [.., G * vdim].
+ * norm_qk == 0 / norm_v == 0 leave out the q/k norm / the value norm; q_norm, k_norm NULL: a norm without a weight; k_pages and
+ * v_pages both NULL: the row holds queries only (a layer that attends over another layer's cache). */
 int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                     int page, const double* freq, const float* q_norm, const float* k_norm, void* q_out, void* k_pages,
-                    void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int act_f32, void* stream);
+                    void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int norm_qk, int norm_v, int act_f32,
+                    void* stream);
+
+/* Optional parts of a softmax attention's score and mask, read by pg_attn_ragged, pg_attn_ragged_mma, pg_attn_decode and
+ * pg_attn_decode_merge (a NULL pointer or an all-zero struct: plain causal attention).  With i the query's position and j a key's:
+ *   window > 0      j is visible only when i - j < window, or j < keep_first (the first keys of a sequence stay visible; they
+ *                   keep their true positions);
+ *   sink            [H] fp32: exp(sink[h]) joins the softmax denominator once, with no key, no value and no scale;
+ *   dist_a, dist_b  [H] fp32 each: the score loses dist_a[h] * log(1 + dist_b[h] * (i - j));
+ *   head_scale      [H] fp32: the scaled score is multiplied by head_scale[h]. */
+typedef struct PgAttnScore {
+  int window;
+  int keep_first;
+  const float* sink;
+  const float* dist_a;
+  const float* dist_b;
+  const float* head_scale;
+} PgAttnScore;
 
 /* Causal attention of every entry's new rows over its cached keys / values (query head h reads k/v head h / (H / G)):
  * s = (q . k) * scale, s <- softcap * tanh(s / softcap) when softcap > 0, softmax over keys 0 .. position, times V; the
@@ -337,7 +373,7 @@ int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* ro
 int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                    int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
-                   long long krow, long long vrow, int gate_per_head, void* stream);
+                   long long krow, long long vrow, int gate_per_head, const PgAttnScore* score, void* stream);
 /* pg_attn_ragged for bf16 activations on the tensor cores (mma.sync m16n8k16): S = Q K^T from the bf16 operands with fp32
  * accumulation; the fp32 probabilities are cut into three bf16 terms each and P V runs as three passes over the bf16 values,
  * so no probability is rounded to bf16.  Head sizes (dim, vdim) in {(32,32), (64,64), (128,128), (64,128), (128,64), (96,64),
@@ -345,16 +381,16 @@ int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, cons
 int pg_attn_ragged_mma(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                        const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                        int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single,
-                       int gate_per_head, void* stream);
+                       int gate_per_head, const PgAttnScore* score, void* stream);
 int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                    const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                    int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,
-                   long long vrow, int gate_per_head, void* stream);
+                   long long vrow, int gate_per_head, const PgAttnScore* score, void* stream);
 
 /* The merge launch of pg_attn_decode on its own: rows of single-token entries from `partial` (fp32 [entries, H, nsplit, vdim + 2]:
  * running max in natural-log units, sum, unnormalised accumulator), times the gate, to out [rows, H * vdim]. */
 int pg_attn_decode_merge(const float* partial, const void* gate, long long ldg, void* out, const int* entry_row0, const int* entry_n,
-                         int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, void* stream);
+                         int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, const PgAttnScore* score, void* stream);
 /* Single-token entries of a latent-attention layer (absorbed form) on the tensor cores, bf16: q [rows, H, dim] against the
  * one-row-per-token cache `pages` [.., page, dim] whose first vdim columns are the values; all heads of a token share one key
  * tile (mma.sync, fp32 probabilities as three bf16 terms, values read from the key tile with ldmatrix.trans).  gate: one scalar
@@ -418,13 +454,16 @@ int pg_latent_pack_kv(const void* up, long long ld_up, const void* pages, const 
  *   pair_row[pair] = its sorted row (-1: identity expert).  fill: int32 [n_real] scratch.
  * pg_moe_gemm: out[row, f] = act(sum_k x[src(row), k] * w[expert(row)][f, k]) for the rows of every tile; src(row) =
  *   sorted_pair[row] / src_div when src_div > 0, else row.  w: [n_real] matrices [F, K] (pitch ldw, expert_stride elements apart).
- *   act: 0 none, 2 relu(x)^2.  x_expert_off / out_expert_off: elements added to x / out per expert index (0 for routed
+ *   act: 0 none, 2 relu(x)^2, 3 gated silu -- the rows of w alternate gate / up (F even) and out has F / 2 columns:
+ *   out[row, f] = silu(acc[2f]) * acc[2f + 1].  x_expert_off / out_expert_off: elements added to x / out per expert index (0 for routed
  *   experts).  With a host-made plan of (batch index, first row, rows) tiles over the SAME rows for every index this is a batched
  *   product whose operands are column slices: out[:, b, :] = x[:, b, :] w[b]^T (per-head projections on the tensor cores).
  * pg_moe_combine: y[t, :] = sum_k weights[t, k] * (pair_row[t, k] < 0 ? h[t, :] : expert_out[pair_row[t, k], :]) + shared_out[t, :]
- *   (shared_out may be NULL). */
+ *   (shared_out may be NULL); shared_gate != NULL: the shared term is multiplied by sigmoid(shared_gate[t * ldsg]);
+ *   accumulate != 0: y[t, :] += instead of = (y is the fp32 residual stream).
+ * pg_moe_route's logit_bias (fp32 [n_all] or NULL) is added to the logits before the softmax. */
 int pg_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int* counts, int tokens, int n_all,
-                 int n_real, int top, int group_count, int group_keep, float scale, void* stream);
+                 int n_real, int top, int group_count, int group_keep, float scale, const float* logit_bias, void* stream);
 int pg_moe_tile_rows(void);
 int pg_moe_plan(const int* counts, const int* ids, int* offsets, int* fill, int* plan, int* sorted_pair, int* pair_row, int pairs,
                 int n_real, int max_tiles, void* stream);
@@ -441,7 +480,8 @@ int pg_moe_gather_rows(const void* x, long long ldx, const int* sorted_pair, con
 int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up, const void* w_down, void* mid, long long ldm, float* eo, long long ldo,
                       const int* counts_host, int n_real, int D, int F, void* stream);
 int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
-                   long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream);
+                   long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32,
+                   const float* shared_gate, long long ldsg, int accumulate, void* stream);
 
 #ifdef __cplusplus
 }

@@ -69,11 +69,11 @@ SIGNATURES = {
     "pg_rmsnorm_gate": [p, p, p, i64, p, i32, i32, f32, i32, p],
     "pg_geglu": [p, i64, p, i64, i32, i32, i32, p],
     "pg_side_gate": [p, i64, p, p, i64, i32, p, i64, i32, i32, i32, i32, p],
-    "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, p],
-    "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, i64, i64, i32, p],
-    "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p],
-    "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i64, i64, i32, p],
-    "pg_attn_decode_merge": [p, p, i64, p, p, p, i32, i32, i32, i32, i32, i32, p],
+    "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, p],
+    "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, i64, i64, i32, p, p],
+    "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p, p],
+    "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i64, i64, i32, p, p],
+    "pg_attn_decode_merge": [p, p, i64, p, p, p, i32, i32, i32, i32, i32, i32, p, p],
     "pg_attn_latent_decode_mma": [p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, f32, p],
     "pg_linear_attn_scan": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_linear_attn_chunked": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
@@ -85,16 +85,24 @@ SIGNATURES = {
     "pg_latent_gather": [p, p, i32, i32, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_latent_pack_kv": [p, i64, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, p],
     "pg_relu2": [p, i64, i32, i32, i32, p],
-    "pg_moe_route": [p, i64, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, p],
+    "pg_moe_route": [p, i64, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, p, p],
     "pg_moe_tile_rows": [],
     "pg_moe_plan": [p, p, p, p, p, p, p, i32, i32, i32, p],
     "pg_moe_gemm": [p, i64, p, i32, p, i64, i64, p, i64, p, i32, i32, i32, i32, i32, i32, i64, i64, p],
     "pg_moe_gather_rows": [p, i64, p, p, i32, p, i64, i32, i32, i32, p],
     "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, p],
-    "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
+    "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p, i64, i32, p],
+    "pg_gemm_simt_bias": [p, i64, p, i64, p, i64, p, i32, i32, i32, i32, i32, i32, p],
+    "pg_layernorm_shift": [p, p, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],
+    "pg_glu": [p, i64, p, i64, i32, i32, i32, f32, f32, i32, p],
 }
 _RESTYPE = {"pg_launch_count": i64}
 
+
+
+class AttnScore(C.Structure):
+    """Mirror of PgAttnScore (include/paligemma_b200.h): the optional parts of an attention's score and mask."""
+    _fields_ = [("window", i32), ("keep_first", i32), ("sink", p), ("dist_a", p), ("dist_b", p), ("head_scale", p)]
 
 
 class GemmFusion(C.Structure):

@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
                                                               const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                               const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                               const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
-                                                              int page, int H, int G, float scale, float softcap, int skip_single, int gate_per_head) {
+                                                              int page, int H, int G, float scale, float softcap, int skip_single, int gate_per_head,
+                                                              PgAttnScore sx) {
   constexpr int KS = DIM / 16, NV = VDIM / 8, QP = DIM + 8, VLD = VDIM + 8;
   static_assert(VDIM % 16 == 0, "value blocks are fetched in pairs");
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
@@ -94,11 +95,26 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
     qa[ks][2] = *reinterpret_cast<const uint32_t*>(Qs + rl * QP + ks * 16 + 8 + 2 * tq);
     qa[ks][3] = *reinterpret_cast<const uint32_t*>(Qs + rh * QP + ks * 16 + 8 + 2 * tq);
   }
-  const int lim_l = r0 + rl < rows ? ctx + (r0 + rl) / gsz : -1;  // last visible key of the lane's two rows
+  const int lim_l = r0 + rl < rows ? ctx + (r0 + rl) / gsz : -1;  // last visible key of the lane's two rows = their queries' positions
   const int lim_h = r0 + rh < rows ? ctx + (r0 + rh) / gsz : -1;
   const int wrow_last = min(rows - 1, r0 + warp * 16 + 15);
   const int wlim = r0 + warp * 16 < rows ? ctx + wrow_last / gsz : -1;
   const int kmax = ctx + (min(rows, r0 + 64) - 1) / gsz;
+  // optional parts of the score: window with kept first keys, per-head multiplier, logarithmic distance penalty
+  const int window = sx.window > 0 ? sx.window : 0x3fffffff, keep = sx.window > 0 ? max(sx.keep_first, 0) : 0;
+  const int head_l = g * gsz + (r0 + rl < rows ? (r0 + rl) % gsz : 0), head_h = g * gsz + (r0 + rh < rows ? (r0 + rh) % gsz : 0);
+  const float sc_l = scale * (sx.head_scale != nullptr ? sx.head_scale[head_l] : 1.f), sc_h = scale * (sx.head_scale != nullptr ? sx.head_scale[head_h] : 1.f);
+  const bool dist = sx.dist_a != nullptr;
+  const float da_l = dist ? sx.dist_a[head_l] : 0.f, da_h = dist ? sx.dist_a[head_h] : 0.f;
+  const float db_l = dist ? sx.dist_b[head_l] : 0.f, db_h = dist ? sx.dist_b[head_h] : 0.f;
+  // key tiles wholly between the kept first keys and the first key inside the window of the CTA's first row are skipped
+  const int keep_end = (keep + 63) & ~63;
+  const int cta_lo = max(0, ctx + r0 / gsz - window + 1) & ~63;
+  const int warp_lo = ctx + min(r0 + warp * 16, rows - 1) / gsz - window + 1;
+  auto next_tile = [&](int k) {
+    const int nx = k + 64;
+    return (nx >= keep_end && nx < cta_lo) ? cta_lo : nx;
+  };
   float oacc[NV][4];
 #pragma unroll
   for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
@@ -126,16 +142,17 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
   };
   const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;  // this lane's row of a 16-key x 16-column block
   int cur = 0;
-  fetch(0, 0);
+  const int k_first = next_tile(-64);
+  fetch(k_first, 0);
   asm volatile("cp.async.commit_group;" ::: "memory");
-  for (int k0 = 0; k0 <= kmax; k0 += 64, cur ^= 1) {
-    if (k0 + 64 <= kmax) fetch(k0 + 64, cur ^ 1);  // that buffer was released by the barrier at the end of the last iteration
+  for (int k0 = k_first; k0 <= kmax; k0 = next_tile(k0), cur ^= 1) {
+    if (next_tile(k0) <= kmax) fetch(next_tile(k0), cur ^ 1);  // that buffer was released by the barrier at the end of the last iteration
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
     const bf16* Ks = Kb + cur * 64 * QP;
     const bf16* Vs = Vb + cur * 64 * VLD;
-    if (k0 <= wlim) {  // else: every row of this warp is past its causal limit
+    if (k0 <= wlim && !(k0 >= keep && k0 + 64 <= warp_lo)) {  // else: no row of this warp sees a key of the tile
     float sacc[8][4];
 #pragma unroll
     for (int nb = 0; nb < 8; ++nb) {
@@ -153,11 +170,13 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
     for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        float sc = sacc[nb][c] * scale;
+        float sc = sacc[nb][c] * ((c & 2) ? sc_h : sc_l);
         if (softcap > 0.f) sc = softcap * tanh32(sc * inv_cap);
-        sc *= 1.4426950408889634f;  // base-2 exponentials below
         const int key = k0 + nb * 8 + 2 * tq + (c & 1);
-        const bool vis = key <= ((c & 2) ? lim_h : lim_l);
+        const int away = ((c & 2) ? lim_h : lim_l) - key;
+        const bool vis = away >= 0 && (away < window || key < keep);
+        if (dist && vis) sc -= ((c & 2) ? da_h : da_l) * log1pf(((c & 2) ? db_h : db_l) * (float)away);
+        sc *= 1.4426950408889634f;  // base-2 exponentials below
         sc = vis ? sc : -INFINITY;
         sacc[nb][c] = sc;
         if (c & 2) mx_h = fmaxf(mx_h, sc); else mx_l = fmaxf(mx_l, sc);
@@ -215,7 +234,13 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
     if (rr >= rows) continue;
     const long long t = row0 + rr / gsz;
     const int head = g * gsz + rr % gsz;
-    const float inv = 1.0f / (half ? l_h : l_l);
+    float lsum = half ? l_h : l_l, osc = 1.f;
+    if (sx.sink != nullptr) {  // the sink joins the denominator once (m is in base-2 units)
+      const float mrow = half ? m_h : m_l, sk = sx.sink[head] * 1.4426950408889634f, mm = fmaxf(mrow, sk);
+      osc = exp2f(mrow - mm);
+      lsum = lsum * osc + exp2f(sk - mm);
+    }
+    const float inv = osc / lsum;
 #pragma unroll
     for (int nv = 0; nv < NV; ++nv) {
       const int col = nv * 8 + 2 * tq;
@@ -418,13 +443,14 @@ int launch_latent(const void* q, const void* pages, const void* gate, long long 
 
 template <int DIM, int VDIM>
 int launch(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0, const int* n, const int* ctx,
-           const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, int gate_per_head, cudaStream_t st) {
+           const int* pt, int max_pages, int page, int entries, int max_n, int H, int G, float scale, float softcap, int skip_single, int gate_per_head,
+           const PgAttnScore& sx, cudaStream_t st) {
   const size_t smem = ((size_t)3 * 64 * (DIM + 8) + (size_t)2 * 64 * (VDIM + 8)) * sizeof(bf16);
   auto kern = attn_ragged_mma_kernel<DIM, VDIM>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   dim3 grid((max_n * (H / G) + 63) / 64, G, entries);
   kern<<<grid, 128, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(kp), static_cast<const bf16*>(vp), static_cast<const bf16*>(gate), ldg,
-                                static_cast<bf16*>(out), row0, n, ctx, pt, max_pages, page, H, G, scale, softcap, skip_single, gate_per_head);
+                                static_cast<bf16*>(out), row0, n, ctx, pt, max_pages, page, H, G, scale, softcap, skip_single, gate_per_head, sx);
   pg_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
@@ -434,8 +460,10 @@ int launch(const void* q, const void* kp, const void* vp, const void* gate, long
 extern "C" int pg_attn_ragged_mma(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                                   const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                                   int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int gate_per_head,
-                                  void* stream) {
+                                  const PgAttnScore* score, void* stream) {
   if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || entries > 65535 || G > 65535) return PG_ERR_ARG;
+  if (score != nullptr && ((score->dist_a == nullptr) != (score->dist_b == nullptr))) return PG_ERR_ARG;
+  const PgAttnScore sx = score != nullptr ? *score : PgAttnScore{};
   // 16-byte row loads and bf16x2 gate / output accesses
   if (((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages) | reinterpret_cast<uintptr_t>(out)) & 15) ||
       (gate != nullptr && !gate_per_head && ((reinterpret_cast<uintptr_t>(gate) & 3) || (ldg & 1))))
@@ -444,7 +472,7 @@ extern "C" int pg_attn_ragged_mma(const void* q, const void* k_pages, const void
 #define PG_MMA(D, V) \
   if (dim == D && vdim == V) \
     return launch<D, V>(q, k_pages, v_pages, gate, ldg, out, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, max_n, H, G, scale, \
-                        softcap, skip_single, gate_per_head, st)
+                        softcap, skip_single, gate_per_head, sx, st)
   PG_MMA(32, 32);
   PG_MMA(96, 64);    // explicit-head form of latent attention: [plain | rotated] keys
   PG_MMA(192, 128);

@@ -56,7 +56,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x, long long ldx, const TI* __restrict__ w, long long ldw,
                                                         TO* __restrict__ out, long long ldo, int T, int F, int K, long long bsx = 0,
-                                                        long long bsw = 0, long long bso = 0) {
+                                                        long long bsw = 0, long long bso = 0, const float* __restrict__ bias = nullptr,
+                                                        int accumulate = 0) {
   __shared__ float xs[16][64 + 4];
   __shared__ float ws[16][64 + 4];
   x += blockIdx.z * bsx;  // batched form: grid.z independent products with their own operand offsets
@@ -89,7 +90,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int t = t0 + ty * 4 + i, f = f0 + tx * 4 + j;
-      if (t < T && f < F) st_f(out, (long long)t * ldo + f, acc[i][j]);
+      if (t < T && f < F) {
+        float v = acc[i][j];
+        if (bias != nullptr) v += bias[f];
+        if (accumulate) v += ld_f(out, (long long)t * ldo + f);
+        st_f(out, (long long)t * ldo + f, v);
+      }
     }
 }
 
@@ -262,6 +268,23 @@ extern "C" int pg_gemm_simt(const void* x, long long ldx, const void* w, long lo
     gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K);
   else if (!in_f32 && !out_f32)
     gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K);
+  else
+    return PG_ERR_ARG;
+  PG_RET();
+}
+
+extern "C" int pg_gemm_simt_bias(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, const float* bias,
+                                 int accumulate, int tokens, int features, int K, int in_f32, int out_f32, void* stream) {
+  if (tokens <= 0 || features <= 0 || K <= 0 || x == nullptr || w == nullptr || out == nullptr) return PG_ERR_ARG;
+  dim3 grid((features + 63) / 64, (tokens + 63) / 64);
+  if (grid.y > 65535) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (in_f32 && out_f32)
+    gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
+  else if (!in_f32 && out_f32)
+    gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
+  else if (!in_f32 && !out_f32)
+    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
   else
     return PG_ERR_ARG;
   PG_RET();

@@ -1,0 +1,171 @@
+// Row kernels of decoders whose layers read ONE residual through two layer norms at once (mixer and feed-forward side by
+// side), with the mixer's input blended with the previous token's:
+//
+//   pg_layernorm_shift   a = LN(x; w1, b1), b = LN(x; w2, b2) from one mean / variance of the row;
+//                        out1[t] = a[t] + (a[t-1] - a[t]) * shift   (a[-1] = 0; a of a sequence's last token is kept in an
+//                        fp32 state slot, so a portion or a decoded token continues where the sequence stopped), out2[t] = b[t]
+//   pg_glu               gated-unit activations on a [gate | up] product that the GEMM epilogue did not fuse
+//
+// LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, statistics in fp32 from the fp32 residual.
+#include "common.cuh"
+#include "paligemma_b200.h"
+
+using bf16 = __nv_bfloat16;
+
+#define PG_ST(s) reinterpret_cast<cudaStream_t>(s)
+#define PG_RET()                                                    \
+  do {                                                              \
+    pg_count_launch(1);                                             \
+    return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA; \
+  } while (0)
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void st_act(T* p, long long i, float v);
+template <>
+__device__ __forceinline__ void st_act<float>(float* p, long long i, float v) { p[i] = v; }
+template <>
+__device__ __forceinline__ void st_act<bf16>(bf16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+template <typename T>
+__device__ __forceinline__ float ld_act(const T* p, long long i);
+template <>
+__device__ __forceinline__ float ld_act<float>(const float* p, long long i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld_act<bf16>(const bf16* p, long long i) { return __bfloat162float(p[i]); }
+
+// sum over the 256 threads of the CTA; every thread gets the result.  `red` = 8 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();  // the previous use of `red` is over
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) s += red[w];
+  return s;
+}
+
+// row -> shared memory, mean and 1 / sqrt(var + eps) (two passes over the staged row: the variance is the mean of the squared
+// deviations, not a difference of large numbers)
+__device__ __forceinline__ void stage_row(const float* __restrict__ src, float* buf, int D, float eps, float* red, float& mean, float& rstd) {
+  float s = 0.f;
+  for (int d = threadIdx.x; d < D; d += 256) {
+    const float v = src[d];
+    buf[d] = v;
+    s += v;
+  }
+  mean = block_sum(s, red) / (float)D;
+  float q = 0.f;
+  for (int d = threadIdx.x; d < D; d += 256) {  // each thread re-reads what it wrote
+    const float c = buf[d] - mean;
+    q = fmaf(c, c, q);
+  }
+  rstd = 1.0f / sqrtf(block_sum(q, red) / (float)D + eps);
+}
+
+// One CTA per row.  Who owns the state slot of entry e: the CTA of the entry's FIRST row -- it reads the slot (the previous
+// token's a) and it alone writes the slot (a of the entry's last row, recomputed here when that is another row), so no other
+// CTA of the launch touches the slot.  Rows inside an entry recompute a of the row before them from x.
+template <typename TO>
+__global__ void __launch_bounds__(256) layernorm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ b1,
+                                                              const float* __restrict__ shift, const float* __restrict__ w2,
+                                                              const float* __restrict__ b2, TO* __restrict__ out1, TO* __restrict__ out2,
+                                                              float* __restrict__ state, const int* __restrict__ pos,
+                                                              const int* __restrict__ row_entry, const int* __restrict__ entry_row0,
+                                                              const int* __restrict__ entry_n, const int* __restrict__ entry_slot, int D, float eps) {
+  extern __shared__ float sm[];
+  float* cur = sm;          // [D] this row
+  float* oth = sm + D;      // [D] the row before / the entry's last row (only with a shift)
+  __shared__ float red[8];
+  const long long t = blockIdx.x;
+  float mean, rstd;
+  stage_row(x + t * D, cur, D, eps, red, mean, rstd);
+  if (shift == nullptr) {
+    for (int d = threadIdx.x; d < D; d += 256) {
+      const float c = (cur[d] - mean) * rstd;
+      st_act(out1, t * D + d, fmaf(c, w1[d], b1[d]));
+      if (out2 != nullptr) st_act(out2, t * D + d, fmaf(c, w2[d], b2[d]));
+    }
+    return;
+  }
+  const int e = row_entry[t], p = pos[t];
+  const int first = entry_row0[e], n = entry_n[e];
+  const bool owner = t == first;
+  float* slot = state + (long long)entry_slot[e] * D;
+  float pm = 0.f, pr = 0.f;
+  const int prev_kind = p == 0 ? 0 : owner ? 1 : 2;  // zeros / the state slot / the row before
+  if (prev_kind == 2) stage_row(x + (t - 1) * D, oth, D, eps, red, pm, pr);
+  for (int d = threadIdx.x; d < D; d += 256) {
+    const float c = (cur[d] - mean) * rstd;
+    const float a = fmaf(c, w1[d], b1[d]);
+    float ap = 0.f;
+    if (prev_kind == 1) ap = slot[d];
+    else if (prev_kind == 2) ap = fmaf((oth[d] - pm) * pr, w1[d], b1[d]);
+    st_act(out1, t * D + d, fmaf(ap - a, shift[d], a));
+    if (out2 != nullptr) st_act(out2, t * D + d, fmaf(c, w2[d], b2[d]));
+    if (owner && n == 1) slot[d] = a;  // the same thread read slot[d] above
+  }
+  if (owner && n > 1) {
+    stage_row(x + (long long)(first + n - 1) * D, oth, D, eps, red, pm, pr);  // block_sum's barriers order this after the loop above
+    for (int d = threadIdx.x; d < D; d += 256) slot[d] = fmaf((oth[d] - pm) * pr, w1[d], b1[d]);
+  }
+}
+
+// kind 1: silu(g) * u;  kind 2: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)
+template <typename TA>
+__global__ void glu_kernel(const TA* __restrict__ gu, long long ldgu, TA* __restrict__ out, long long ldo, int F, long long total, int kind,
+                           float limit, float alpha) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / F;
+    const int f = (int)(i % F);
+    float g = ld_act(gu, t * ldgu + f), u = ld_act(gu, t * ldgu + F + f), y;
+    if (kind == 2) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    } else {
+      y = g / (1.0f + expf(-g)) * u;
+    }
+    st_act(out, t * ldo + f, y);
+  }
+}
+
+}  // namespace
+
+extern "C" int pg_layernorm_shift(const float* x, const float* w1, const float* b1, const float* shift, const float* w2, const float* b2, void* out1,
+                                  void* out2, float* state, const int* pos, const int* row_entry, const int* entry_row0, const int* entry_n,
+                                  const int* entry_slot, int rows, int D, float eps, int out_f32, void* stream) {
+  if (rows <= 0 || D <= 0 || x == nullptr || w1 == nullptr || b1 == nullptr || out1 == nullptr) return PG_ERR_ARG;
+  if ((out2 != nullptr) && (w2 == nullptr || b2 == nullptr)) return PG_ERR_ARG;
+  if (shift != nullptr && (state == nullptr || pos == nullptr || row_entry == nullptr || entry_row0 == nullptr || entry_n == nullptr || entry_slot == nullptr))
+    return PG_ERR_ARG;
+  const size_t smem = (size_t)(shift != nullptr ? 2 : 1) * D * sizeof(float);
+  if (smem > 200 * 1024) return PG_ERR_ARG;
+  cudaStream_t st = PG_ST(stream);
+  if (out_f32) {
+    auto kern = layernorm_shift_kernel<float>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+    kern<<<rows, 256, smem, st>>>(x, w1, b1, shift, w2, b2, static_cast<float*>(out1), static_cast<float*>(out2), state, pos, row_entry, entry_row0,
+                                  entry_n, entry_slot, D, eps);
+  } else {
+    auto kern = layernorm_shift_kernel<bf16>;
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
+    kern<<<rows, 256, smem, st>>>(x, w1, b1, shift, w2, b2, static_cast<bf16*>(out1), static_cast<bf16*>(out2), state, pos, row_entry, entry_row0,
+                                  entry_n, entry_slot, D, eps);
+  }
+  PG_RET();
+}
+
+extern "C" int pg_glu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int kind, float limit, float alpha, int act_f32,
+                      void* stream) {
+  if (rows <= 0 || F <= 0 || (kind != 1 && kind != 2)) return PG_ERR_ARG;
+  const long long total = (long long)rows * F;
+  const int blocks = (int)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
+  if (act_f32)
+    glu_kernel<float><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(gu), ldgu, static_cast<float*>(out), ldo, F, total, kind, limit, alpha);
+  else
+    glu_kernel<bf16><<<blocks, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(gu), ldgu, static_cast<bf16*>(out), ldo, F, total, kind, limit, alpha);
+  PG_RET();
+}

@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
                                                            const int* __restrict__ row_entry, const int* __restrict__ page_table, int max_pages,
                                                            int page, const double* __restrict__ freq, const float* __restrict__ qn,
                                                            const float* __restrict__ kn, TA* __restrict__ q_out, TA* __restrict__ k_pages,
-                                                           TA* __restrict__ v_pages, int H, int G, int dim, int vdim, int rot, float eps) {
+                                                           TA* __restrict__ v_pages, int H, int G, int dim, int vdim, int rot, float eps,
+                                                           int norm_qk, int norm_v) {
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const long long t = blockIdx.x;
   const int p = pos[t];
@@ -73,20 +74,24 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const long long pg_row = (long long)page_table[(long long)row_entry[t] * max_pages + p / page] * page + p % page;
   const TA* row = qkv + t * ld;
-  for (int vec = warp; vec < H + 2 * G; vec += nw) {
+  const int nvec = k_pages != nullptr ? H + 2 * G : H;  // a layer that borrows another layer's keys / values prepares its queries only
+  for (int vec = warp; vec < nvec; vec += nw) {
     const bool is_q = vec < H, is_k = !is_q && vec < H + G;
     const int n = (is_q || is_k) ? dim : vdim;
     const long long off = is_q ? (long long)vec * dim : is_k ? (long long)H * dim + (long long)(vec - H) * dim
                                                             : (long long)(H + G) * dim + (long long)(vec - H - G) * vdim;
     // lane <-> pairs (2i, 2i+1): a rotation never needs another lane's element; an odd last element is a pair with a zero
-    float ss = 0.f;
-    for (int d = 2 * lane; d < n; d += 64) {
-      const float a = ldf(row, off + d), b2 = d + 1 < n ? ldf(row, off + d + 1) : 0.f;
-      ss = fmaf(a, a, fmaf(b2, b2, ss));
+    float inv = 1.0f;
+    if ((is_q || is_k) ? norm_qk : norm_v) {
+      float ss = 0.f;
+      for (int d = 2 * lane; d < n; d += 64) {
+        const float a = ldf(row, off + d), b2 = d + 1 < n ? ldf(row, off + d + 1) : 0.f;
+        ss = fmaf(a, a, fmaf(b2, b2, ss));
+      }
+      ss = wsum(ss);
+      inv = 1.0f / sqrtf(ss / (float)n + eps);
     }
-    ss = wsum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-    const float* w = is_q ? qn : kn;
+    const float* w = is_q ? qn : kn;  // NULL: a norm without a weight
     TA* dst = is_q   ? q_out + t * ((long long)H * dim) + (long long)vec * dim
               : is_k ? k_pages + pg_row * ((long long)G * dim) + (long long)(vec - H) * dim
                      : v_pages + pg_row * ((long long)G * vdim) + (long long)(vec - H - G) * vdim;
@@ -94,8 +99,10 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
       const bool two = d + 1 < n;
       float a = ldf(row, off + d) * inv, b2 = two ? ldf(row, off + d + 1) * inv : 0.f;
       if (is_q || is_k) {
-        a *= w[d];
-        if (two) b2 *= w[d + 1];
+        if (w != nullptr) {
+          a *= w[d];
+          if (two) b2 *= w[d + 1];
+        }
         if (d < rot) {  // rot is even: the pair is rotated as a whole
           const float c = cs[d >> 1], sn = cs[rot / 2 + (d >> 1)];
           const float ra = a * c - b2 * sn, rb = b2 * c + a * sn;
@@ -120,13 +127,14 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
                                                           const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                           const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
                                                           int page, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single,
-                                                          long long krow, long long vrow, int gate_per_head, int alias) {
+                                                          long long krow, long long vrow, int gate_per_head, int alias, PgAttnScore sx) {
   const int e = blockIdx.z, g = blockIdx.y, gsz = H / G;
   const int n = entry_n[e], ctx = entry_ctx[e], row0 = entry_row0[e];
   if (skip_single && n == 1) return;
   const int rows = n * gsz;
   const int r0 = blockIdx.x * 32;
   if (r0 >= rows) return;
+  const int window = sx.window > 0 ? sx.window : 0x3fffffff, keep = sx.window > 0 ? max(sx.keep_first, 0) : 0;
   const int dimp = (dim + 3) & ~3, ks = dimp + 4;
   extern __shared__ __align__(16) float sm[];
   float* Qs = sm;                    // [32][dimp]
@@ -143,7 +151,8 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
     Qs[i] = v;
   }
   float m[4], l[4], o[4][VC];
-  int lim[4];  // last visible key of the row (-1: row does not exist)
+  int lim[4];  // last visible key of the row = the query's position (-1: row does not exist)
+  float hsc[4], da[4], db[4];  // per-row head constants of the score
   int wlim = -1;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -153,11 +162,23 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
     const int rr = r0 + warp * 4 + i;
     lim[i] = rr < rows ? ctx + rr / gsz : -1;
     wlim = max(wlim, lim[i]);
+    const int head = g * gsz + (rr < rows ? rr % gsz : 0);
+    hsc[i] = scale * (sx.head_scale != nullptr ? sx.head_scale[head] : 1.f);
+    da[i] = sx.dist_a != nullptr ? sx.dist_a[head] : 0.f;
+    db[i] = sx.dist_a != nullptr ? sx.dist_b[head] : 0.f;
   }
   const int last_row = min(rows, r0 + 32) - 1;
   const int kmax = ctx + last_row / gsz;  // last key any row of this CTA sees
+  // first key inside the window of the CTA's / the warp's first row (later rows start later); tiles wholly between the kept first
+  // keys and that key are skipped
+  const int cta_lo = ctx + r0 / gsz - window + 1;
+  const int warp_lo = ctx + min(r0 + warp * 4, rows - 1) / gsz - window + 1;
   const int* pt = page_table + (long long)e * max_pages;
   for (int k0 = 0; k0 <= kmax; k0 += 32) {
+    if (k0 >= keep && k0 + 32 <= cta_lo) {
+      k0 = (cta_lo / 32) * 32 - 32;  // uniform over the CTA
+      continue;
+    }
     __syncthreads();
     for (int i = threadIdx.x; i < 32 * dimp; i += 256) {
       const int r = i / dimp, d = i % dimp, j = k0 + r;
@@ -173,7 +194,7 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
         Vs[i] = v;
       }
     __syncthreads();
-    if (k0 > wlim) continue;  // every row of this warp is past its causal limit
+    if (k0 > wlim || (k0 >= keep && k0 + 32 <= warp_lo)) continue;  // no row of this warp sees a key of the tile
     float s[4] = {0.f, 0.f, 0.f, 0.f};
     const float* kr = Ks + lane * ks;
     const float* qw = Qs + warp * 4 * dimp;
@@ -188,9 +209,11 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
     float* pw = Ps + warp * 128;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float sc = s[i] * scale;
+      float sc = s[i] * hsc[i];
       if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
-      const bool vis = k0 + lane <= lim[i];
+      const int key = k0 + lane;
+      const bool vis = key <= lim[i] && (lim[i] - key < window || key < keep);
+      if (sx.dist_a != nullptr && vis) sc -= da[i] * log1pf(db[i] * (float)(lim[i] - key));
       sc = vis ? sc : -INFINITY;
       const float mn = fmaxf(m[i], wmax(sc));
       float pr = 0.f, corr = 1.f;
@@ -227,7 +250,13 @@ __global__ void __launch_bounds__(256) attn_ragged_kernel(const TA* __restrict__
     if (rr >= rows) continue;
     const long long t = row0 + rr / gsz;
     const int head = g * gsz + rr % gsz;
-    const float inv = 1.0f / l[i];
+    float osc = 1.f;
+    if (sx.sink != nullptr) {  // the sink joins the denominator once; the numerator has no term for it
+      const float sk = sx.sink[head], mm = fmaxf(m[i], sk);
+      osc = expf(m[i] - mm);
+      l[i] = l[i] * osc + expf(sk - mm);
+    }
+    const float inv = osc / l[i];
 #pragma unroll
     for (int c = 0; c < VC; ++c) {
       const int col = lane + 32 * c;
@@ -274,7 +303,7 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
                                                           const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
                                                           const int* __restrict__ entry_ctx, const int* __restrict__ page_table, int max_pages,
                                                           int page, int H, int G, int dim, int vdim, float scale, float softcap, long long krow,
-                                                          long long vrow, int gate_per_head) {
+                                                          long long vrow, int gate_per_head, PgAttnScore sx) {
   constexpr int NO = VEC ? 8 * VC : 2 * VC;  // accumulator columns per lane
   const int e = blockIdx.z, g = blockIdx.y, split = blockIdx.x, nsplit = gridDim.x, gsz = H / G;
   if (entry_n[e] != 1) return;
@@ -296,18 +325,29 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
   __syncthreads();
   const int* pt = page_table + (long long)e * max_pages;
   const int ntiles = ctx / 32 + 1;  // keys 0 .. ctx
+  // with a window only the tiles of the kept first keys [0, nk) and of the window [t_lo, ntiles) are walked
+  const int window = sx.window > 0 ? sx.window : 0x3fffffff, keep = sx.window > 0 ? max(sx.keep_first, 0) : 0;
+  const int t_lo = max(0, ctx - window + 1) / 32;
+  const int nkeep = min(min((keep + 31) / 32, ntiles), t_lo);
+  const int nwalk = nkeep + ntiles - t_lo;
   for (int rb = 0; rb < gsz; rb += 4) {
     const int nr = min(4, gsz - rb);
     float m[4], l[4], o[4][NO];
+    float hsc[4], da[4], db[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       m[i] = -INFINITY; l[i] = 0.f;
 #pragma unroll
       for (int c = 0; c < NO; ++c) o[i][c] = 0.f;
+      const int head = g * gsz + min(rb + i, gsz - 1);
+      hsc[i] = scale * (sx.head_scale != nullptr ? sx.head_scale[head] : 1.f);
+      da[i] = sx.dist_a != nullptr ? sx.dist_a[head] : 0.f;
+      db[i] = sx.dist_a != nullptr ? sx.dist_b[head] : 0.f;
     }
-    for (int it = split * 8 + warp; it < ntiles; it += nsplit * 8) {
+    for (int walk = split * 8 + warp; walk < nwalk; walk += nsplit * 8) {
+      const int it = walk < nkeep ? walk : t_lo + (walk - nkeep);
       const int j = it * 32 + lane;
-      const bool vis = j <= ctx;
+      const bool vis = j <= ctx && (ctx - j < window || j < keep);
       float s[4] = {0.f, 0.f, 0.f, 0.f};
       if (vis) {
         const TA* kr = k_pages + ((long long)pt[j / page] * page + j % page) * krow + (long long)g * dim;
@@ -336,10 +376,11 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
       float* pw = Pw + warp * 128;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float sc = s[i] * scale;
+        float sc = s[i] * hsc[i];
         if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+        if (sx.dist_a != nullptr && vis) sc -= da[i] * log1pf(db[i] * (float)(ctx - j));
         sc = vis ? sc : -INFINITY;
-        const float mn = fmaxf(m[i], wmax(sc));  // key it * 32 <= ctx is always visible: mn is finite
+        const float mn = fmaxf(m[i], wmax(sc));  // every walked tile holds a visible key: mn is finite
         const float pr = vis ? expf(sc - mn) : 0.f;
         const float corr = expf(m[i] - mn);
         l[i] = l[i] * corr + wsum(pr);
@@ -440,6 +481,11 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const TA* __restrict__
         }
       const int head = g * gsz + rb + i;
       if (nsplit == 1) {
+        if (sx.sink != nullptr) {
+          const float sk = sx.sink[head], mm = fmaxf(M, sk), f = expf(M - mm);
+          acc *= f;
+          ls = ls * f + expf(sk - mm);
+        }
         float v = acc / ls;
         if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (gate_per_head ? (long long)head : (long long)head * vdim + col)));
         stf(out, t * ((long long)H * vdim) + (long long)head * vdim + col, v);
@@ -458,7 +504,7 @@ static inline int merge_threads(int vdim) { return vdim <= 64 ? 64 : vdim <= 128
 template <typename TA>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, const TA* __restrict__ gate, long long ldg, TA* __restrict__ out,
                                          const int* __restrict__ entry_row0, const int* __restrict__ entry_n, int H, int vdim, int nsplit,
-                                         int gate_per_head) {
+                                         int gate_per_head, const float* __restrict__ sink) {
   const int e = blockIdx.y, head = blockIdx.x;
   if (entry_n[e] != 1) return;
   const long long t = entry_row0[e];
@@ -474,6 +520,11 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, cons
         acc = fmaf(f, pp[s * (vdim + 2) + 2 + col], acc);
         ls = fmaf(f, pp[s * (vdim + 2) + 1], ls);
       }
+    }
+    if (sink != nullptr) {
+      const float sk = sink[head], mm = fmaxf(M, sk), f = expf(M - mm);
+      acc *= f;
+      ls = ls * f + expf(sk - mm);
     }
     float v = acc / ls;
     if (gate != nullptr) v *= sigmoidf(ldf(gate, t * ldg + (gate_per_head ? (long long)head : (long long)head * vdim + col)));
@@ -723,17 +774,19 @@ __global__ void __launch_bounds__(256, 2) linear_attn_chunked_kernel(const TA* _
 
 extern "C" int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                                int page, const double* freq, const float* q_norm, const float* k_norm, void* q_out, void* k_pages,
-                               void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int act_f32, void* stream) {
+                               void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int norm_qk, int norm_v,
+                               int act_f32, void* stream) {
   if (rows <= 0 || H <= 0 || G <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || page <= 0) return PG_ERR_ARG;
+  if ((k_pages == nullptr) != (v_pages == nullptr)) return PG_ERR_ARG;
   const size_t smem = (size_t)(rot_dims + 2) * sizeof(float);
   if (act_f32)
     attn_prepare_kernel<float><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const float*>(qkv), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                   q_norm, k_norm, static_cast<float*>(q_out), static_cast<float*>(k_pages),
-                                                                  static_cast<float*>(v_pages), H, G, dim, vdim, rot_dims, eps);
+                                                                  static_cast<float*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v);
   else
     attn_prepare_kernel<bf16><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const bf16*>(qkv), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                  q_norm, k_norm, static_cast<bf16*>(q_out), static_cast<bf16*>(k_pages),
-                                                                 static_cast<bf16*>(v_pages), H, G, dim, vdim, rot_dims, eps);
+                                                                 static_cast<bf16*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v);
   PG_RET();
 }
 
@@ -741,7 +794,7 @@ template <typename TA, int VC>
 static int launch_attn_ragged(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, const int* row0,
                               const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int max_n, int H, int G,
                               int dim, int vdim, float scale, float softcap, int skip_single, long long krow, long long vrow, int gate_per_head,
-                              cudaStream_t st) {
+                              const PgAttnScore& sx, cudaStream_t st) {
   const int dimp = (dim + 3) & ~3;
   // one latent row serves as key and value (one k/v head, values = leading key columns): the tile is staged once
   const int alias = (kp == vp && G == 1 && krow == vrow && vdim <= dim) ? 1 : 0;
@@ -752,22 +805,24 @@ static int launch_attn_ragged(const void* q, const void* kp, const void* vp, con
   dim3 grid((max_n * (H / G) + 31) / 32, G, entries);
   kern<<<grid, 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp), static_cast<const TA*>(gate), ldg,
                                 static_cast<TA*>(out), row0, n, ctx, pt, max_pages, page, H, G, dim, vdim, scale, softcap, skip_single, krow, vrow,
-                                gate_per_head, alias);
+                                gate_per_head, alias, sx);
   PG_RET();
 }
 
 extern "C" int pg_attn_ragged(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                               int entries, int max_n, int H, int G, int dim, int vdim, float scale, float softcap, int skip_single, int act_f32,
-                              long long krow, long long vrow, int gate_per_head, void* stream) {
+                              long long krow, long long vrow, int gate_per_head, const PgAttnScore* score, void* stream) {
   if (entries <= 0 || max_n <= 0 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 512 || entries > 65535 || G > 65535)
     return PG_ERR_ARG;
+  if (score != nullptr && ((score->dist_a == nullptr) != (score->dist_b == nullptr))) return PG_ERR_ARG;
+  const PgAttnScore sx = score != nullptr ? *score : PgAttnScore{};
   if (krow <= 0) krow = (long long)G * dim;
   if (vrow <= 0) vrow = (long long)G * vdim;
   cudaStream_t st = PG_ST(stream);
 #define PG_ATTN(TA, VC) \
   return launch_attn_ragged<TA, VC>(q, k_pages, v_pages, gate, ldg, out, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, max_n, \
-                                    H, G, dim, vdim, scale, softcap, skip_single, krow, vrow, gate_per_head, st)
+                                    H, G, dim, vdim, scale, softcap, skip_single, krow, vrow, gate_per_head, sx, st)
   if (act_f32) {
     if (vdim <= 64) PG_ATTN(float, 2);
     if (vdim <= 128) PG_ATTN(float, 4);
@@ -860,7 +915,7 @@ template <typename TA, int VC, bool VEC>
 static int launch_attn_decode(const void* q, const void* kp, const void* vp, const void* gate, long long ldg, void* out, float* partial,
                               const int* row0, const int* n, const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H,
                               int G, int dim, int vdim, float scale, float softcap, long long krow, long long vrow, int gate_per_head,
-                              cudaStream_t st) {
+                              const PgAttnScore& sx, cudaStream_t st) {
   const int gsz = H / G, dimp = (dim + 7) & ~7;
   const size_t smem = ((size_t)gsz * dimp + 8 * 128 + 64 + (size_t)32 * vdim) * sizeof(float);
   if (smem > 200 * 1024) return PG_ERR_ARG;
@@ -868,36 +923,39 @@ static int launch_attn_decode(const void* q, const void* kp, const void* vp, con
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   kern<<<dim3(nsplit, G, entries), 256, smem, st>>>(static_cast<const TA*>(q), static_cast<const TA*>(kp), static_cast<const TA*>(vp),
                                                      static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), partial, row0, n, ctx, pt, max_pages, page,
-                                                     H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head);
+                                                     H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head, sx);
   pg_count_launch(1);
   if (nsplit > 1) {
     attn_decode_merge_kernel<TA><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const TA*>(gate), ldg, static_cast<TA*>(out), row0, n, H, vdim, nsplit,
-                                                                  gate_per_head);
+                                                                  gate_per_head, sx.sink);
     pg_count_launch(1);
   }
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
 
 extern "C" int pg_attn_decode_merge(const float* partial, const void* gate, long long ldg, void* out, const int* entry_row0, const int* entry_n,
-                                    int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, void* stream) {
+                                    int entries, int nsplit, int H, int vdim, int gate_per_head, int act_f32, const PgAttnScore* score, void* stream) {
   if (entries <= 0 || entries > 65535 || nsplit <= 0 || H <= 0 || vdim <= 0 || partial == nullptr) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
+  const float* sink = score != nullptr ? score->sink : nullptr;
   if (act_f32)
     attn_decode_merge_kernel<float><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const float*>(gate), ldg, static_cast<float*>(out), entry_row0, entry_n,
-                                                                     H, vdim, nsplit, gate_per_head);
+                                                                     H, vdim, nsplit, gate_per_head, sink);
   else
     attn_decode_merge_kernel<bf16><<<dim3(H, entries), merge_threads(vdim), 0, st>>>(partial, static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), entry_row0, entry_n, H,
-                                                                    vdim, nsplit, gate_per_head);
+                                                                    vdim, nsplit, gate_per_head, sink);
   PG_RET();
 }
 
 extern "C" int pg_attn_decode(const void* q, const void* k_pages, const void* v_pages, const void* gate, long long ldg, void* out, float* partial,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages, int page,
                               int entries, int nsplit, int H, int G, int dim, int vdim, float scale, float softcap, int act_f32, long long krow,
-                              long long vrow, int gate_per_head, void* stream) {
+                              long long vrow, int gate_per_head, const PgAttnScore* score, void* stream) {
   if (entries <= 0 || nsplit <= 0 || nsplit > 64 || H <= 0 || G <= 0 || (H % G) != 0 || dim <= 0 || vdim <= 0 || vdim > 512 || entries > 65535 ||
       G > 65535 || (nsplit > 1 && partial == nullptr))
     return PG_ERR_ARG;
+  if (score != nullptr && ((score->dist_a == nullptr) != (score->dist_b == nullptr))) return PG_ERR_ARG;
+  const PgAttnScore sx = score != nullptr ? *score : PgAttnScore{};
   if (krow <= 0) krow = (long long)G * dim;
   if (vrow <= 0) vrow = (long long)G * vdim;
   cudaStream_t st = PG_ST(stream);
@@ -906,7 +964,7 @@ extern "C" int pg_attn_decode(const void* q, const void* k_pages, const void* v_
                    ((reinterpret_cast<uintptr_t>(k_pages) & 15) == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0);
 #define PG_ATTD(TA, VC, VEC) \
   return launch_attn_decode<TA, VC, VEC>(q, k_pages, v_pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, \
-                                         entries, nsplit, H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head, st)
+                                         entries, nsplit, H, G, dim, vdim, scale, softcap, krow, vrow, gate_per_head, sx, st)
   if (act_f32) {
     if (vec && vdim <= 64) PG_ATTD(float, 1, true);
     if (vec) PG_ATTD(float, 2, true);

@@ -60,7 +60,8 @@ __device__ __forceinline__ void wargmax(float& v, int& i) {
 // One warp per token; probabilities and choice scores of the token in shared memory (2 * n_all floats per warp).
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction,
                                                         int* __restrict__ ids, float* __restrict__ weights, int* __restrict__ counts, int T,
-                                                        int n_all, int n_real, int top, int group_count, int group_keep, float scale) {
+                                                        int n_all, int n_real, int top, int group_count, int group_keep, float scale,
+                                                        const float* __restrict__ logit_bias) {
   extern __shared__ float sm[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * 4 + warp;
@@ -69,10 +70,14 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   float* choice = prob + n_all;
   const float* z = logits + (long long)t * ld;
   float m = -INFINITY;
-  for (int i = lane; i < n_all; i += 32) m = fmaxf(m, z[i]);
+  for (int i = lane; i < n_all; i += 32) {
+    const float zi = z[i] + (logit_bias != nullptr ? logit_bias[i] : 0.f);
+    prob[i] = zi;
+    m = fmaxf(m, zi);
+  }
   m = wmaxf(m);
   float s = 0.f;
-  for (int i = lane; i < n_all; i += 32) { const float e = expf(z[i] - m); prob[i] = e; s += e; }
+  for (int i = lane; i < n_all; i += 32) { const float e = expf(prob[i] - m); prob[i] = e; s += e; }
   s = wsumf(s);
   for (int i = lane; i < n_all; i += 32) {
     const float p = prob[i] / s;
@@ -227,6 +232,19 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ x,
     }
     __syncthreads();
   }
+  if (act == 3) {  // rows of w alternate gate / up: out[:, f / 2] = silu(gate) * up, both held by this thread
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int r = 4 * ty + i, f = f0 + tx * 4 + j;
+        if (r < nr && f + 1 < F) {
+          const float gv = acc[i][j];
+          stm(out, (long long)(r0 + r) * ldo + f / 2, gv / (1.0f + expf(-gv)) * acc[i][j + 1]);
+        }
+      }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -340,6 +358,21 @@ __global__ void __launch_bounds__(128) moe_gemm_mma_kernel(const bf16* __restric
       }
     }
   }
+  if (act == 3) {  // rows of w alternate gate / up: accumulator columns (2 tq, 2 tq + 1) are one output feature's pair
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int ni = 0; ni < NI; ++ni)
+#pragma unroll
+        for (int c = 0; c < 4; c += 2) {
+          const int r = 32 * wm + 16 * mi + gq + ((c & 2) ? 8 : 0), f = f0 + (BN / 2) * wn + 8 * ni + 2 * tq;
+          if (r < nr && f + 1 < F) {
+            const float gv = acc[mi][ni][c];
+            stm(out, (long long)(r0 + r) * ldo + f / 2, gv / (1.0f + expf(-gv)) * acc[mi][ni][c + 1]);
+          }
+        }
+    return;
+  }
 #pragma unroll
   for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
@@ -382,8 +415,10 @@ __global__ void moe_gather_rows_kernel(const TA* __restrict__ x, long long ldx, 
 template <typename TA>
 __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long long ldy, const int* __restrict__ pair_row, const int* __restrict__ ids,
                                    const float* __restrict__ weights, const TA* __restrict__ h, long long ldh, const float* __restrict__ shared_out,
-                                   long long lds, float* __restrict__ y, int D, int top) {
+                                   long long lds, float* __restrict__ y, int D, int top, const float* __restrict__ shared_gate, long long ldsg,
+                                   int accumulate) {
   const long long t = blockIdx.x;
+  const float sgate = shared_gate != nullptr ? 1.0f / (1.0f + expf(-shared_gate[t * ldsg])) : 1.0f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -392,15 +427,15 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, long lo
       const float v = row < 0 ? ldm(h, t * ldh + d) : expert_out[(long long)row * ldy + d];
       acc = fmaf(wgt, v, acc);
     }
-    if (shared_out != nullptr) acc += shared_out[t * lds + d];
-    y[t * D + d] = acc;
+    if (shared_out != nullptr) acc = fmaf(sgate, shared_out[t * lds + d], acc);
+    y[t * D + d] = accumulate ? y[t * D + d] + acc : acc;
   }
 }
 
 }  // namespace
 
 extern "C" int pg_moe_route(const float* logits, long long ld, const float* correction, int* ids, float* weights, int* counts, int tokens, int n_all,
-                            int n_real, int top, int group_count, int group_keep, float scale, void* stream) {
+                            int n_real, int top, int group_count, int group_keep, float scale, const float* logit_bias, void* stream) {
   if (tokens <= 0 || n_all <= 0 || n_real < 0 || n_real > n_all || top <= 0 || top > n_all) return PG_ERR_ARG;
   if (group_count > 1 && (n_all % group_count != 0 || group_keep <= 0 || group_keep > group_count || group_count > 256)) return PG_ERR_ARG;
   if (group_count > 1 && top > (long long)group_keep * (n_all / group_count)) return PG_ERR_ARG;
@@ -409,7 +444,7 @@ extern "C" int pg_moe_route(const float* logits, long long ld, const float* corr
   cudaStream_t st = PG_ST(stream);
   if (n_real > 0 && cudaMemsetAsync(counts, 0, (size_t)n_real * sizeof(int), st) != cudaSuccess) return PG_ERR_CUDA;
   moe_route_kernel<<<(tokens + 3) / 4, 128, smem, st>>>(logits, ld, correction, ids, weights, counts, tokens, n_all, n_real, top, group_count, group_keep,
-                                                        scale);
+                                                        scale, logit_bias);
   PG_RET();
 }
 
@@ -428,7 +463,7 @@ extern "C" int pg_moe_plan(const int* counts, const int* ids, int* offsets, int*
 extern "C" int pg_moe_gemm(const void* x, long long ldx, const int* sorted_pair, int src_div, const void* w, long long expert_stride, long long ldw,
                            void* out, long long ldo, const int* plan, int max_tiles, int F, int K, int act, int in_f32, int out_f32, long long x_expert_off,
                            long long out_expert_off, void* stream) {
-  if (max_tiles <= 0 || max_tiles > 65535 || F <= 0 || K <= 0 || src_div < 0) return PG_ERR_ARG;
+  if (max_tiles <= 0 || max_tiles > 65535 || F <= 0 || K <= 0 || src_div < 0 || (act == 3 && (F & 1))) return PG_ERR_ARG;
   dim3 grid((F + 63) / 64, max_tiles);
   cudaStream_t st = PG_ST(stream);
   // bf16 operands whose rows can be fetched in 16-byte pieces go to the tensor cores
@@ -532,12 +567,13 @@ extern "C" int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up
 }
 
 extern "C" int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
-                              long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32, void* stream) {
+                              long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32,
+                              const float* shared_gate, long long ldsg, int accumulate, void* stream) {
   if (tokens <= 0 || D <= 0 || top <= 0) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
   if (act_f32)
-    moe_combine_kernel<float><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const float*>(h), ldh, shared_out, lds, y, D, top);
+    moe_combine_kernel<float><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const float*>(h), ldh, shared_out, lds, y, D, top, shared_gate, ldsg, accumulate);
   else
-    moe_combine_kernel<bf16><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const bf16*>(h), ldh, shared_out, lds, y, D, top);
+    moe_combine_kernel<bf16><<<tokens, 256, 0, st>>>(expert_out, ldy, pair_row, ids, weights, static_cast<const bf16*>(h), ldh, shared_out, lds, y, D, top, shared_gate, ldsg, accumulate);
   PG_RET();
 }

@@ -4,12 +4,19 @@
                           rotary positions with long-wavelength frequency rescaling, weightless value norm, tanh soft cap,
                           sigmoid output gate
   LightningAttention      decayed linear attention with a per-sequence fp32 state, gated RMS norm over the joined heads
+  WindowedSoftmaxAttention grouped-query softmax attention over a sliding window of the paged cache; optional, each a parameter:
+                          projection biases, weightless q/k RMS norm, partial interleaved rotation, a logarithmic distance penalty,
+                          a per-head score multiplier, a softmax sink, kept first keys, a per-head sigmoid output gate, keys and
+                          values borrowed from an earlier layer's cache
   GegluFeedForward        W_down(gelu_tanh(W_gate h) * W_up h)
+  GluFeedForward          W_down(act(W_gate h) * W_up h) with act = silu, or the clamped form min(g, c) sigmoid(a min(g, c)) (clamp(u) + 1);
+                          optional biases
   TokenSideInput          a per-layer, per-token low-dimensional embedding gated by a projection of the residual stream
 
 Every sub-layer gets its weights from a name -> tensor dict (`take(name)` pops and checks the shape), packs them once for a
 `Precision`, says what it keeps per sequence (`cache_spec`), and maps the step's rows h [T, D] (activation type) to
-y [T, D] fp32; the block around it owns norms and the residual stream.
+y [T, D] fp32; the block around it owns norms and the residual stream.  The newer sub-layers take `resid=` (the fp32 residual
+rows): their last projection then adds into it in the GEMM epilogue instead of returning y.
 """
 import ctypes as C
 import math
@@ -70,6 +77,92 @@ class GatedSoftmaxAttention:
         att = prec.empty(b.T, H * vdim)
         gate = proj[:, (H + G) * dim + G * vdim:]
         seq_ops.attn_ragged(q, kp, vp, gate, att, b, H, G, dim, vdim, self.scale, self.softcap, PAGE)
+        return seq_ops.linear(att, self.w_o, torch.empty(b.T, self.D, device="cuda", dtype=torch.float32))
+
+
+class WindowedSoftmaxAttention:
+    """q = W_q h (+ b), k, v likewise; optional weightless RMS norm of q and k per head; optional rotation of the first rot_dims
+    dimensions; score(i, j) = (q_i . k_j) * scale * temp_h - r1_h * log(1 + r2_h * (i - j)); key j is visible to query i when
+    j <= i and (i - j < window or j < keep_first); softmax over the visible keys, with exp(sink_h) joining the denominator when
+    the layer has a sink; head output times sigmoid((W_g h)_h) when it has a gate; then W_o.
+
+    kv_from = j: the layer has no key / value projections and attends over layer j's cached keys and values (as layer j left
+    them, after its norm and rotation) with its own queries, window and score."""
+
+    def __init__(self, width, heads, kv_heads, dim, vdim, scale, eps, window=None, keep_first=0, bias=False, qk_norm=False, rot_dims=0,
+                 rot_base=10000.0, distance_penalty=False, temperature=False, sink=False, head_gate=False, kv_from=None):
+        if heads % kv_heads:
+            raise ValueError("query heads must be a multiple of key/value heads")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError("rotary dimensions must be even and at most the head size")
+        if window is not None and int(window) <= 0:
+            raise ValueError("a window holds at least the token itself")
+        self.D, self.H, self.G, self.dim, self.vdim = int(width), int(heads), int(kv_heads), int(dim), int(vdim)
+        self.scale, self.eps, self.window, self.keep_first = float(scale), float(eps), (int(window) if window is not None else None), int(keep_first)
+        self.bias, self.qk_norm, self.rot_dims = bool(bias), bool(qk_norm), int(rot_dims)
+        self.distance_penalty, self.temperature, self.sink, self.head_gate = bool(distance_penalty), bool(temperature), bool(sink), bool(head_gate)
+        self.kv_from = None if kv_from is None else int(kv_from)
+        self.freq = rotary_frequencies(rot_base, rot_dims) if rot_dims else torch.zeros(1, dtype=torch.float64)
+
+    def cache_spec(self):
+        return None if self.kv_from is not None else ("kv", self.G * self.dim, self.G * self.vdim)
+
+    def load(self, take, pre):
+        H, G, dim, vdim, D = self.H, self.G, self.dim, self.vdim, self.D
+        w = dict(q=take(pre + "q", (H * dim, D)))
+        if self.bias:
+            w["qb"] = take(pre + "q.b", (H * dim,))
+        if self.kv_from is None:
+            w["k"], w["v"] = take(pre + "k", (G * dim, D)), take(pre + "v", (G * vdim, D))
+            if self.bias:
+                w["kb"], w["vb"] = take(pre + "k.b", (G * dim,)), take(pre + "v.b", (G * vdim,))
+        if self.distance_penalty:
+            w["r1"], w["r2"] = take(pre + "r1", (H,)), take(pre + "r2", (H,))
+        if self.temperature:
+            w["temp"] = take(pre + "temp", (H,))
+        if self.sink:
+            w["sink"] = take(pre + "sink", (H,))
+        if self.head_gate:
+            w["g"] = take(pre + "g", (H, D))
+        w["o"] = take(pre + "o", (D, H * vdim))
+        self.w = w
+
+    def pack(self, prec):
+        w, H = self.w, self.H
+        f32 = dict(device="cuda", dtype=torch.float32)
+        parts = [w["q"]] + ([w["k"], w["v"]] if self.kv_from is None else []) + ([w["g"]] if self.head_gate else [])
+        rows = sum(t.shape[0] for t in parts)
+        pad = (-rows) % 8  # zero rows up to a multiple of 8: a shape the tensor-core product takes
+        self.w_in = torch.zeros(rows + pad, self.D, device="cuda", dtype=prec.dtype)
+        self.w_in[:rows] = torch.cat(parts, 0).to("cuda", prec.dtype)
+        self.gate_col = rows - H if self.head_gate else None
+        self.b_in = None
+        if self.bias:
+            self.b_in = torch.zeros(rows + pad, **f32)
+            bs = torch.cat([w["qb"]] + ([w["kb"], w["vb"]] if self.kv_from is None else [])).to(**f32)
+            self.b_in[:bs.numel()] = bs
+        self.w_o = w["o"].to("cuda", prec.dtype).contiguous()
+        self.freq_d = self.freq.to("cuda")
+
+        def vec(name):
+            return w[name].to(**f32).contiguous() if name in w else None
+
+        self.score = seq_ops.ScoreOptions(H, self.window, self.keep_first, sink=vec("sink"), dist_a=vec("r1"), dist_b=vec("r2"), head_scale=vec("temp"))
+
+    def __call__(self, h, b, store, li, prec, resid=None):
+        H, G, dim, vdim = self.H, self.G, self.dim, self.vdim
+        proj = seq_ops.linear(h, self.w_in, prec.empty(b.T, self.w_in.shape[0]), bias=self.b_in)
+        q = prec.empty(b.T, H * dim)
+        own = self.kv_from is None
+        src = li if own else self.kv_from
+        kp, vp = store.k_pages[src], store.v_pages[src]
+        seq_ops.attn_prepare(proj, b, self.freq_d, None, None, q, kp if own else None, vp if own else None, H, G, dim, vdim, self.rot_dims, self.eps,
+                             PAGE, norm_qk=self.qk_norm, norm_v=False)
+        att = prec.empty(b.T, H * vdim)
+        gate = proj[:, self.gate_col:] if self.head_gate else None
+        seq_ops.attn_ragged(q, kp, vp, gate, att, b, H, G, dim, vdim, self.scale, 0.0, PAGE, gate_per_head=True, score=self.score)
+        if resid is not None:
+            return seq_ops.linear_add(att, self.w_o, resid)
         return seq_ops.linear(att, self.w_o, torch.empty(b.T, self.D, device="cuda", dtype=torch.float32))
 
 
@@ -142,6 +235,39 @@ class GegluFeedForward:
             mid = prec.empty(T, self.F)
             seq_ops.geglu(gu, mid)
         return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class GluFeedForward:
+    """W_down (act(W_gate h) * W_up h) (+ biases).  activation "silu": silu(g) * u; "clamped": g' = min(g, limit),
+    u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)."""
+
+    def __init__(self, width, ff, activation="silu", limit=0.0, alpha=1.0, bias=False):
+        if activation not in ("silu", "clamped"):
+            raise ValueError(f"unknown gated activation {activation!r}")
+        self.D, self.F, self.kind = int(width), int(ff), seq_ops.GLU_CLAMPED if activation == "clamped" else seq_ops.GLU_SILU
+        self.limit, self.alpha, self.bias = float(limit), float(alpha), bool(bias)
+
+    def load(self, take, pre):
+        F, D = self.F, self.D
+        self.w = dict(gate=take(pre + "gate", (F, D)), up=take(pre + "up", (F, D)), down=take(pre + "down", (D, F)))
+        if self.bias:
+            self.w.update(gate_b=take(pre + "gate.b", (F,)), up_b=take(pre + "up.b", (F,)), down_b=take(pre + "down.b", (D,)))
+
+    def pack(self, prec):
+        w = self.w
+        f32 = dict(device="cuda", dtype=torch.float32)
+        self.w_gu = torch.cat([w["gate"], w["up"]], 0).to("cuda", prec.dtype).contiguous()
+        self.w_down = w["down"].to("cuda", prec.dtype).contiguous()
+        self.b_gu = torch.cat([w["gate_b"], w["up_b"]]).to(**f32).contiguous() if self.bias else None
+        self.b_down = w["down_b"].to(**f32).contiguous() if self.bias else None
+
+    def __call__(self, h, b, prec, resid=None):
+        T = h.shape[0]
+        gu = seq_ops.linear(h, self.w_gu, prec.empty(T, 2 * self.F), bias=self.b_gu)
+        mid = seq_ops.glu(gu, prec.empty(T, self.F), self.kind, self.limit, self.alpha)
+        if resid is not None:
+            return seq_ops.linear_add(mid, self.w_down, resid, bias=self.b_down)
+        return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32), bias=self.b_down)
 
 
 class TokenSideInput:
@@ -264,34 +390,61 @@ class SquaredReluFeedForward:
 
 
 class RoutedFeedForward:
-    """Mixture of squared-relu experts.  Router: p = softmax(W_r h) in fp32 over `experts + identity` outputs; the choice uses
+    """Mixture of experts.  Router: p = softmax(W_r h + b_r) in fp32 over `experts + identity` outputs; the choice uses
     p + correction, limited to the `group_keep` best of `group_count` runs of neighbouring outputs; the `top` chosen outputs
-    weigh in with p / sum(p chosen) * scale.  The last `identity` outputs return h itself.  A shared expert (optional) is added
-    for every token."""
+    weigh in with p / sum(p chosen) * scale (without a correction that is the softmax over the chosen logits alone, chosen by
+    the largest logits).  The last `identity` outputs return h itself.  A shared expert (optional) is added for every token,
+    times sigmoid(w_sg . h) when it is gated.  activation "relu2": experts W_down relu(W_up h)^2; "silu_glu": experts
+    W_down (silu(W_gate h) * W_up h)."""
 
-    def __init__(self, width, experts, identity, top, group_count, group_keep, scale, expert_ff, shared_ff):
+    def __init__(self, width, experts, identity, top, group_count, group_keep, scale, expert_ff, shared_ff, activation="relu2",
+                 correction=True, router_bias=False, shared_gate=False):
+        if activation not in ("relu2", "silu_glu"):
+            raise ValueError(f"unknown expert activation {activation!r}")
         self.D, self.n_real, self.n_all, self.top = width, int(experts), int(experts) + int(identity), int(top)
         self.group_count, self.group_keep, self.scale, self.F = int(group_count), int(group_keep), float(scale), int(expert_ff)
         if self.group_count > 1 and self.n_all % self.group_count:
             raise ValueError("router outputs must divide into equal groups")
-        self.shared = SquaredReluFeedForward(width, int(shared_ff)) if shared_ff else None
+        self.glu, self.has_correction, self.router_bias = activation == "silu_glu", bool(correction), bool(router_bias)
+        if not shared_ff:
+            self.shared = None
+        else:
+            self.shared = GluFeedForward(width, int(shared_ff), "silu") if self.glu else SquaredReluFeedForward(width, int(shared_ff))
+        self.shared_gate = bool(shared_gate) and self.shared is not None
 
     def load(self, take, pre):
         D, F = self.D, self.F
-        self.w = dict(router=take(pre + "router", (self.n_all, D)), correction=take(pre + "correction", (self.n_all,)),
-                      up=[take(f"{pre}e{e}.up", (F, D)) for e in range(self.n_real)], down=[take(f"{pre}e{e}.down", (D, F)) for e in range(self.n_real)])
+        self.w = dict(router=take(pre + "router", (self.n_all, D)), up=[take(f"{pre}e{e}.up", (F, D)) for e in range(self.n_real)],
+                      down=[take(f"{pre}e{e}.down", (D, F)) for e in range(self.n_real)])
+        if self.glu:
+            self.w["gate"] = [take(f"{pre}e{e}.gate", (F, D)) for e in range(self.n_real)]
+        if self.has_correction:
+            self.w["correction"] = take(pre + "correction", (self.n_all,))
+        if self.router_bias:
+            self.w["router_b"] = take(pre + "router.b", (self.n_all,))
         if self.shared is not None:
             self.shared.load(take, pre + "shared.")
+        if self.shared_gate:
+            self.w["sg"] = take(pre + "shared.sg", (1, D))
 
     def pack(self, prec):
         w = self.w
         # router rows padded with zeros to a multiple of 8: a shape the tensor-core product takes (the choice only reads n_all columns)
-        n_pad = (self.n_all + 7) // 8 * 8
+        # (the shared expert's gate vector is one more row of the same product: column n_all of the logits)
+        n_pad = (self.n_all + int(self.shared_gate) + 7) // 8 * 8
         self.w_router = torch.zeros(n_pad, self.D, device="cuda", dtype=prec.dtype)
         self.w_router[:self.n_all] = w["router"].to("cuda", prec.dtype)
-        self.correction = w["correction"].to("cuda", torch.float32).contiguous()
+        if self.shared_gate:
+            self.w_router[self.n_all] = w["sg"][0].to("cuda", prec.dtype)
+        self.correction = w["correction"].to("cuda", torch.float32).contiguous() if self.has_correction else None
+        self.router_b = w["router_b"].to("cuda", torch.float32).contiguous() if self.router_bias else None
         if self.n_real:
-            self.w_up = torch.stack(w["up"]).to("cuda", prec.dtype).contiguous()
+            if self.glu:
+                # rows alternate gate / up: an accumulator pair of the grouped product's epilogue is one output feature
+                gu = torch.stack([torch.stack(w["gate"]), torch.stack(w["up"])], 2)  # [n, F, 2, D]
+                self.w_up = gu.reshape(self.n_real, 2 * self.F, self.D).to("cuda", prec.dtype).contiguous()
+            else:
+                self.w_up = torch.stack(w["up"]).to("cuda", prec.dtype).contiguous()
             self.w_down = torch.stack(w["down"]).to("cuda", prec.dtype).contiguous()
         if self.shared is not None:
             self.shared.pack(prec)
@@ -300,7 +453,7 @@ class RoutedFeedForward:
     DENSE_SEGMENT_ROWS = 256
 
     def _dense_segments(self, T, prec):
-        return (not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
+        return (not self.glu and not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
                 and not torch.cuda.is_current_stream_capturing())
 
     def expert_products(self, h, plan, counts, prec):
@@ -317,17 +470,21 @@ class RoutedFeedForward:
                                                     eo.data_ptr(), eo.stride(0), C.addressof(per), self.n_real, self.D, self.F, _lib.stream()),
                        "pg_moe_dense_runs")
             return eo
-        mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_RELU2)
+        mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_SILU_GLU if self.glu else seq_ops.ACT_RELU2)
         return seq_ops.moe_gemm(mid, plan, self.w_down, torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32), gather=False)
 
-    def __call__(self, h, b, prec):
+    def __call__(self, h, b, prec, resid=None):
         T = h.shape[0]
         z = seq_ops.linear(h, self.w_router, torch.empty(T, self.w_router.shape[0], device="cuda", dtype=torch.float32))
-        ids, wts, counts = seq_ops.moe_route(z[:, :self.n_all], self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale)
+        ids, wts, counts = seq_ops.moe_route(z[:, :self.n_all], self.correction, self.n_real, self.top, self.group_count, self.group_keep, self.scale,
+                                             logit_bias=self.router_b)
         plan = seq_ops.MoePlan(ids, counts, max(1, self.n_real))
         eo = self.expert_products(h, plan, counts, prec) if self.n_real else None
         sh = self.shared(h, b, prec) if self.shared is not None else None
-        return seq_ops.moe_combine(eo, plan, ids, wts, h, sh, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+        sg = z[:, self.n_all:self.n_all + 1] if self.shared_gate else None
+        if resid is not None:
+            return seq_ops.moe_combine(eo, plan, ids, wts, h, sh, resid, shared_gate=sg, accumulate=True)
+        return seq_ops.moe_combine(eo, plan, ids, wts, h, sh, torch.empty(T, self.D, device="cuda", dtype=torch.float32), shared_gate=sg)
 
 
 class StreamCoefficients:

@@ -58,7 +58,13 @@ def _load_pukerax(path, dtype=torch.bfloat16, **kw):
     return load_pukerax(path, dtype)
 
 
+def _load_kovusun(path, dtype=torch.bfloat16, **kw):
+    from .modeling_kovusun import load_kovusun
+    return load_kovusun(path, dtype)
+
+
 for _n in ("paligemma", "PaliGemmaForConditionalGeneration"):
     register(_n, _load_paligemma)
 register("Mapedra", _load_mapedra)
 register("Pukerax", _load_pukerax)
+register("Kovusun", _load_kovusun)

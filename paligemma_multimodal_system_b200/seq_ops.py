@@ -132,11 +132,11 @@ def _aligned(t, n=16):
     return t.data_ptr() % n == 0
 
 
-ACT_NONE, ACT_GELU, ACT_RELU2 = 0, 1, 2
+ACT_NONE, ACT_GELU, ACT_RELU2, ACT_SILU_GLU = 0, 1, 2, 3  # ACT_SILU_GLU: grouped products only (gate / up rows alternate)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_NONE):
-    """out[t, f] = act(sum_k x[t, k] w[f, k]).  x, w share a type (bf16 / fp32); out is bf16 or fp32.  bf16 operands go to the
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_NONE, bias: Optional[torch.Tensor] = None):
+    """out[t, f] = act(sum_k x[t, k] w[f, k] + bias[f]) (bias fp32 or None).  x, w share a type (bf16 / fp32); out is bf16 or fp32.  bf16 operands go to the
     tcgen05 kernel when TMA can describe them (16-byte pitches and bases), everything else to the plain-FMA kernel.
     act = ACT_RELU2 (relu squared; out in the operands' type): in the tensor-core kernel's bf16 epilogue, else a pass of its own."""
     T, K = x.shape
@@ -147,8 +147,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_N
             and out.stride(0) % 8 == 0 and _aligned(x) and _aligned(w) and _aligned(out)):
         assert act == ACT_NONE or out.dtype == torch.bfloat16
         if act != ACT_NONE:
-            return _lib.gemm(x, w, out, mode=_lib.EPI_BF16, act_gelu=act, swap=1 if T <= 128 else 0)
-        if T <= 128 and out.dtype == torch.float32:
+            return _lib.gemm(x, w, out, mode=_lib.EPI_BF16, act_gelu=act, swap=1 if T <= 128 else 0, bias=bias)
+        if T <= 128 and out.dtype == torch.float32 and bias is None:
             # few rows, few 128-feature tiles (output and down projections): split K over CTAs so that the whole GPU streams the
             # weights; the fp32 partials are red.add-ed into the zeroed output (as the framework's other decode GEMMs do)
             tiles, kb = (F + 127) // 128, (K + 63) // 64
@@ -156,15 +156,65 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_N
             if split > 1:
                 out.zero_()
                 return _lib.gemm(x, w, out, mode=_lib.EPI_ATOMIC_F32, swap=1, split_k=split)
-        return _lib.gemm(x, w, out, mode=_lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_BF16, swap=1 if T <= 128 else 0)
+        return _lib.gemm(x, w, out, mode=_lib.EPI_F32 if out.dtype == torch.float32 else _lib.EPI_BF16, swap=1 if T <= 128 else 0, bias=bias)
     if x.dtype == torch.float32 and out.dtype != torch.float32:
         raise ValueError("fp32 operands produce fp32 outputs")
-    _lib.check(_lib.lib().pg_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), T, F, K,
-                                       int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == F and bias.is_contiguous()
+        _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), bias.data_ptr(), 0,
+                                                T, F, K, int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt_bias")
+    else:
+        _lib.check(_lib.lib().pg_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), T, F, K,
+                                           int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt")
     if act == ACT_RELU2:
         _lib.check(_lib.lib().pg_relu2(out.data_ptr(), out.stride(0), T, F, int(out.dtype == torch.float32), _lib.stream()), "pg_relu2")
     elif act != ACT_NONE:
         raise ValueError("the plain-FMA product has no fused activation but relu squared")
+    return out
+
+
+def linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """resid[t, f] += sum_k x[t, k] w[f, k] + bias[f]: a projection that ends in the fp32 residual stream.  bf16 operands TMA can
+    describe: the tcgen05 kernel adds the residual in its epilogue (or red.adds split-K partials into it when there are few
+    tiles); everything else: the plain-FMA kernel reads and rewrites the residual element."""
+    T, K = x.shape
+    F = w.shape[0]
+    assert x.dtype == w.dtype and w.shape[1] == K and resid.shape == (T, F) and resid.dtype == torch.float32 and resid.is_contiguous()
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and F % 8 == 0 and _aligned(x) and _aligned(w)
+            and _aligned(resid)):
+        return _lib.gemm_residual(x, w, resid, bias=bias)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == F and bias.is_contiguous())
+    _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), resid.data_ptr(), resid.stride(0), _lib.ptr(bias), 1,
+                                            T, F, K, int(x.dtype == torch.float32), 1, _lib.stream()), "pg_gemm_simt_bias")
+    return resid
+
+
+def layernorm_shift(x, w1, b1, out1, eps, shift=None, state=None, b: "StepBatch" = None, w2=None, b2=None, out2=None):
+    """out1 = LN(x; w1, b1) -- blended with the previous token's when `shift` [D] is given (state: fp32 [slots, D], the batch says which
+    row continues which sequence) -- and out2 = LN(x; w2, b2) from the same statistics.  x fp32 [rows, D]; outputs bf16 or fp32."""
+    rows, D = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and out1.is_contiguous() and out1.shape == x.shape
+    for t in (w1, b1, shift, w2, b2):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == D)
+    assert out2 is None or (out2.is_contiguous() and out2.shape == x.shape and out2.dtype == out1.dtype and w2 is not None and b2 is not None)
+    if shift is not None:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous() and state.shape[-1] == D and b is not None and b.T == rows
+    _lib.check(_lib.lib().pg_layernorm_shift(x.data_ptr(), w1.data_ptr(), b1.data_ptr(), _lib.ptr(shift), _lib.ptr(w2), _lib.ptr(b2), out1.data_ptr(),
+                                             _lib.ptr(out2), _lib.ptr(state), *((b.pos.data_ptr(), b.row_entry.data_ptr(), b.row0.data_ptr(),
+                                                                                 b.n.data_ptr(), b.slot.data_ptr()) if shift is not None else (0, 0, 0, 0, 0)),
+                                             rows, D, float(eps), int(out1.dtype == torch.float32), _lib.stream()), "pg_layernorm_shift")
+
+
+GLU_SILU, GLU_CLAMPED = 1, 2
+
+
+def glu(gu, out, kind, limit=0.0, alpha=1.0):
+    """out[t, f] from the [gate | up] product gu [rows, 2F]: GLU_SILU silu(g) * u; GLU_CLAMPED min(g, limit) * sigmoid(alpha * .) * (clamp(u) + 1)."""
+    rows, F = out.shape
+    assert gu.shape[1] == 2 * F and gu.dtype == out.dtype and gu.stride(1) == 1 and out.stride(1) == 1
+    _lib.check(_lib.lib().pg_glu(gu.data_ptr(), gu.stride(0), out.data_ptr(), out.stride(0), rows, F, int(kind), float(limit), float(alpha),
+                                 int(out.dtype == torch.float32), _lib.stream()), "pg_glu")
     return out
 
 
@@ -207,12 +257,34 @@ def side_gate(z, tokens, table, col0, out, n):
                                        out.stride(0), rows, int(n), n_pad, int(out.dtype == torch.float32), _lib.stream()), "pg_side_gate")
 
 
-def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_pages, H, G, dim, vdim, rot_dims, eps, page):
-    assert qkv.stride(1) == 1 and freq.dtype == torch.float64 and k_pages.dtype == qkv.dtype == q_out.dtype
+def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_pages, H, G, dim, vdim, rot_dims, eps, page, norm_qk=True, norm_v=True):
+    """q_norm / k_norm None: norms without a weight; norm_qk / norm_v False: no q/k norm / no value norm; k_pages and v_pages None: the
+    rows hold queries only (the layer attends over another layer's cache)."""
+    assert qkv.stride(1) == 1 and freq.dtype == torch.float64 and qkv.dtype == q_out.dtype and (k_pages is None) == (v_pages is None)
+    assert k_pages is None or k_pages.dtype == qkv.dtype
     _lib.check(_lib.lib().pg_attn_prepare(qkv.data_ptr(), qkv.stride(0), b.pos.data_ptr(), b.row_entry.data_ptr(), b.page_table.data_ptr(),
-                                          b.max_pages, page, freq.data_ptr(), q_norm.data_ptr(), k_norm.data_ptr(), q_out.data_ptr(),
-                                          k_pages.data_ptr(), v_pages.data_ptr(), b.T, H, G, dim, vdim, rot_dims, float(eps),
-                                          int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
+                                          b.max_pages, page, freq.data_ptr(), _lib.ptr(q_norm), _lib.ptr(k_norm), q_out.data_ptr(),
+                                          _lib.ptr(k_pages), _lib.ptr(v_pages), b.T, H, G, dim, vdim, rot_dims, float(eps), int(bool(norm_qk)),
+                                          int(bool(norm_v)), int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
+
+
+class ScoreOptions:
+    """The optional parts of a softmax attention's score and mask, as the kernels read them (PgAttnScore): a sliding window of
+    `window` keys (None: all) that keeps the first `keep_first` keys of the sequence visible, a per-head sink logit in the softmax
+    denominator, a penalty dist_a[h] * log(1 + dist_b[h] * distance), a per-head score multiplier.  Tensors: fp32 [H] on the device."""
+
+    def __init__(self, heads, window=None, keep_first=0, sink=None, dist_a=None, dist_b=None, head_scale=None):
+        for t in (sink, dist_a, dist_b, head_scale):
+            assert t is None or (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads)
+        assert (dist_a is None) == (dist_b is None)
+        self.window = int(window) if window else 0
+        self.keep_first = int(keep_first) if self.window else 0
+        self._keep = (sink, dist_a, dist_b, head_scale)  # the struct holds raw pointers
+        self.c = _lib.AttnScore(self.window, self.keep_first, _lib.ptr(sink), _lib.ptr(dist_a), _lib.ptr(dist_b), _lib.ptr(head_scale))
+
+    def visible_keys(self, context):
+        """Upper bound of the keys a query at position `context` reads."""
+        return context + 1 if not self.window else min(context + 1, self.window + self.keep_first)
 
 
 # head sizes (dim, vdim) the tensor-core attention kernel is instantiated for
@@ -224,14 +296,18 @@ LATENT_MMA_SIZES = {(96, 64), (160, 128), (192, 128), (288, 256)}
 
 
 def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True,
-                krow=0, vrow=0, gate_per_head=False, only_singles=False, skip_singles=False):
+                krow=0, vrow=0, gate_per_head=False, only_singles=False, skip_singles=False, score: Optional["ScoreOptions"] = None):
     """Entries with several new rows go to a tiled kernel -- on the tensor cores for bf16 activations and the usual head
     sizes (fp32 probabilities as three bf16 terms), plain fp32 FMAs otherwise -- and entries with ONE new row (decoded tokens)
     to the key-split kernel (`decode_kernel=False`: everything through the tiled kernel).  Same arithmetic, other summation
     order.  krow / vrow: elements per cache row when it is not G * dim / G * vdim (a latent cache: one row is key and value);
     gate_per_head: the gate holds one scalar per head instead of one per output element; only_singles / skip_singles: rows of
-    entries with several new tokens / with one new token are left alone (another form computes them)."""
+    entries with several new tokens / with one new token are left alone (another form computes them).  score: window, sink, distance
+    penalty and per-head multiplier (ScoreOptions; None: plain causal attention)."""
+    import ctypes as C
     L, f32 = _lib.lib(), int(q.dtype == torch.float32)
+    sx = C.addressof(score.c) if score is not None else 0
+    reach = score.visible_keys(b.max_single_ctx) if score is not None else b.max_single_ctx + 1  # keys a decoded token reads at most
     ldg = 0 if gate is None else gate.stride(0)
     gph = int(bool(gate_per_head))
     singles = b.singles if (decode_kernel or skip_singles) else 0
@@ -242,15 +318,15 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
             and (gate is None or gph or (ldg % 2 == 0 and gate.data_ptr() % 4 == 0))):
         _lib.check(L.pg_attn_ragged_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
                                         b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
-                                        float(scale), float(softcap or 0.0), int(singles > 0), gph, _lib.stream()), "pg_attn_ragged_mma")
+                                        float(scale), float(softcap or 0.0), int(singles > 0), gph, sx, _lib.stream()), "pg_attn_ragged_mma")
     elif singles < b.E:
         _lib.check(L.pg_attn_ragged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(),
                                     b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, b.max_n, H, G, dim, vdim,
-                                    float(scale), float(softcap or 0.0), int(singles > 0), f32, int(krow), int(vrow), gph, _lib.stream()),
+                                    float(scale), float(softcap or 0.0), int(singles > 0), f32, int(krow), int(vrow), gph, sx, _lib.stream()),
                    "pg_attn_ragged")
     latent = (k_pages.data_ptr() == v_pages.data_ptr() and G == 1 and krow == vrow == dim and k_pages.shape[-1] == dim)
     if (singles and not skip_singles and latent and tensor_cores and not f32 and (dim, vdim) in LATENT_MMA_SIZES and softcap in (0, 0.0, None)
-            and (gate is None or gph)):
+            and (gate is None or gph) and score is None):
         # one-row-per-token cache, every head of a token against the same key tile: tensor cores
         tiles = b.max_single_ctx // 64 + 1
         nsplit = max(1, min(tiles, (4 * _lib.num_sms()) // (singles * -(-H // 64)), 32))  # measured: 4 CTAs per SM beat 2 despite the larger merge
@@ -260,15 +336,15 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
                                                float(scale), _lib.stream()), "pg_attn_latent_decode_mma")
         if nsplit > 1:
             _lib.check(L.pg_attn_decode_merge(partial.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.E, nsplit, H,
-                                              vdim, gph, 0, _lib.stream()), "pg_attn_decode_merge")
+                                              vdim, gph, 0, 0, _lib.stream()), "pg_attn_decode_merge")
     elif singles and not skip_singles:
-        tiles = b.max_single_ctx // 32 + 1
+        tiles = (reach - 1) // 32 + 1
         # enough CTAs for two waves, but at least two 32-key tiles for every warp of a CTA
         nsplit = max(1, min(-(-2 * _lib.num_sms() // (G * singles)), tiles // 16, 32))
         partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
         _lib.check(L.pg_attn_decode(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial),
                                     b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit,
-                                    H, G, dim, vdim, float(scale), float(softcap or 0.0), f32, int(krow), int(vrow), gph, _lib.stream()),
+                                    H, G, dim, vdim, float(scale), float(softcap or 0.0), f32, int(krow), int(vrow), gph, sx, _lib.stream()),
                    "pg_attn_decode")
 
 
@@ -378,15 +454,15 @@ def dense_view(b: StepBatch) -> StepBatch:
 
 
 # ---- routed feed-forward ---------------------------------------------------------------------------------------------
-def moe_route(logits, correction, n_real, top, group_count, group_keep, scale):
-    """logits fp32 [T, n_all] -> ids int32 [T, top], weights fp32 [T, top], counts int32 [n_real] (device)."""
+def moe_route(logits, correction, n_real, top, group_count, group_keep, scale, logit_bias=None):
+    """logits fp32 [T, n_all] (+ logit_bias fp32 [n_all]) -> ids int32 [T, top], weights fp32 [T, top], counts int32 [n_real] (device)."""
     T, n_all = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     ids = torch.empty(T, top, device="cuda", dtype=torch.int32)
     wts = torch.empty(T, top, device="cuda", dtype=torch.float32)
     counts = torch.empty(max(1, n_real), device="cuda", dtype=torch.int32)
     _lib.check(_lib.lib().pg_moe_route(logits.data_ptr(), logits.stride(0), _lib.ptr(correction), ids.data_ptr(), wts.data_ptr(), counts.data_ptr(), T,
-                                       n_all, n_real, top, int(group_count), int(group_keep), float(scale), _lib.stream()), "pg_moe_route")
+                                       n_all, n_real, top, int(group_count), int(group_keep), float(scale), _lib.ptr(logit_bias), _lib.stream()), "pg_moe_route")
     return ids, wts, counts
 
 
@@ -412,7 +488,8 @@ def moe_gemm(x, plan: MoePlan, w, out, gather, act=0):
     """out[row] = act(x[src(row)] @ w[expert(row)].T) over the plan's tiles; gather: x rows are tokens (src = pair // top),
     else x rows are already in sorted order.  w [n_real, F, K] contiguous."""
     n_real, F, K = w.shape
-    assert w.is_contiguous() and x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == K and out.shape[1] == F
+    assert w.is_contiguous() and x.dtype == w.dtype and x.stride(1) == 1 and out.stride(1) == 1 and x.shape[1] == K
+    assert out.shape[1] == (F // 2 if act == ACT_SILU_GLU else F)
     _lib.check(_lib.lib().pg_moe_gemm(x.data_ptr(), x.stride(0), plan.sorted_pair.data_ptr(), plan.top if gather else 0, w.data_ptr(), F * K, K,
                                       out.data_ptr(), out.stride(0), plan.plan.data_ptr(), plan.max_tiles, F, K, int(act),
                                       int(x.dtype == torch.float32), int(out.dtype == torch.float32), 0, 0, _lib.stream()), "pg_moe_gemm")
@@ -427,13 +504,17 @@ def moe_gather_rows(x, plan: MoePlan, out):
     return out
 
 
-def moe_combine(expert_out, plan: MoePlan, ids, weights, h, shared_out, y):
+def moe_combine(expert_out, plan: MoePlan, ids, weights, h, shared_out, y, shared_gate=None, accumulate=False):
+    """y[t] (+)= sum_k weights[t, k] * expert row (or h[t] for an identity expert) + sigmoid(shared_gate[t]) * shared_out[t]; shared_gate:
+    fp32 logits, one per token (a strided column view), None: the shared term counts fully; accumulate: add into y."""
     T, D = y.shape
+    assert shared_gate is None or (shared_gate.dtype == torch.float32 and shared_gate.shape[0] == T)
     assert y.dtype == torch.float32 and y.is_contiguous() and h.stride(1) == 1
     assert expert_out is None or (expert_out.dtype == torch.float32 and expert_out.stride(1) == 1)
     _lib.check(_lib.lib().pg_moe_combine(_lib.ptr(expert_out), 0 if expert_out is None else expert_out.stride(0), plan.pair_row.data_ptr(), ids.data_ptr(),
                                          weights.data_ptr(), h.data_ptr(), h.stride(0), _lib.ptr(shared_out), 0 if shared_out is None else shared_out.stride(0),
-                                         y.data_ptr(), T, D, plan.top, int(h.dtype == torch.float32), _lib.stream()), "pg_moe_combine")
+                                         y.data_ptr(), T, D, plan.top, int(h.dtype == torch.float32), _lib.ptr(shared_gate),
+                                         0 if shared_gate is None else shared_gate.stride(0), int(bool(accumulate)), _lib.stream()), "pg_moe_combine")
     return y
 
 
