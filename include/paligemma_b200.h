@@ -349,7 +349,7 @@ int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* ro
  *                   keep their true positions);
  *   sink            [H] fp32: exp(sink[h]) joins the softmax denominator once, with no key, no value and no scale;
  *   dist_a, dist_b  [H] fp32 each: the score loses dist_a[h] * log(1 + dist_b[h] * (i - j));
- *   head_scale      [H] fp32: the scaled score is multiplied by head_scale[h]. */
+ *   head_scale      [H] fp32: the scaled dot product is multiplied by head_scale[h] (before the distance term is taken off). */
 typedef struct PgAttnScore {
   int window;
   int keep_first;

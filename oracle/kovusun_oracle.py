@@ -72,12 +72,37 @@ def keys_values(h, w, pre, kind, m, eps):
     return k, v
 
 
+def attend(q, keys, vals, scale, size=None, keep=0, sink=None, r1=None, r2=None, temp=None, first_pos=0):
+    """q [T, H, dim] at positions first_pos .. first_pos + T - 1 over keys [N, G, dim] / vals [N, G, vd] at positions 0 .. N - 1
+    -> [T, H, vd].  One (query, head) at a time, a plain softmax over the listed visible keys (the sink as an extra logit)."""
+    T, H = q.shape[:2]
+    G = keys.shape[1]
+    out = torch.zeros(T, H, vals.shape[-1], dtype=q.dtype)
+    for t in range(T):
+        i = first_pos + t
+        js = [j for j in range(min(i + 1, keys.shape[0])) if visible(i, j, size, keep)]
+        jt = torch.tensor(js)
+        dist = (i - jt).to(q.dtype)
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (keys[jt, g] @ q[t, hh]) * float(scale)
+            if temp is not None:
+                s = s * temp[hh]
+            if r1 is not None:  # (no layer type has both a temperature and a penalty; here the penalty is not scaled by the temperature)
+                s = s - r1[hh] * torch.log(1.0 + r2[hh] * dist)
+            if sink is not None:
+                p = torch.softmax(torch.cat([s, sink[hh].reshape(1).to(s.dtype)]), 0)[:-1]
+            else:
+                p = torch.softmax(s, 0)
+            out[t, hh] = (p[:, None] * vals[jt, g]).sum(0)
+    return out
+
+
 def attention(h, w, pre, kind, m, eps, kv):
     """h [T, D] -> [T, D]; kv = (keys, values) of this layer or of the layer it borrows from."""
     T = h.shape[0]
-    H, G, dim, vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    H, dim, vd = int(m["heads"]), int(m["dim"]), int(m["vdim"])
     mask = m.get("mask") or {}
-    size, keep = mask.get("size"), int(mask.get("keep_first", 0))
     q = h @ w[pre + "q"].T
     if kind == "attention":
         q = q + w[pre + "q.b"]
@@ -86,25 +111,10 @@ def attention(h, w, pre, kind, m, eps, kv):
         q = unit_rms(q, eps)
     if kind == "attention_3" and m.get("rot"):
         q = torch.stack([rotate_pairs(q[t], t, m["rot"]["base"], int(m["rot"]["dims"])) for t in range(T)])
-    keys, vals = kv
-    out = torch.zeros(T, H, vd, dtype=h.dtype)
-    for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, size, keep)]
-        jt = torch.tensor(js)
-        dist = (i - jt).to(h.dtype)
-        for hh in range(H):
-            g = hh // (H // G)
-            s = (keys[jt, g] @ q[i, hh]) * float(m["scale"])
-            if kind == "attention":
-                s = s - w[pre + "r1"][hh] * torch.log(1.0 + w[pre + "r2"][hh] * dist)
-            if kind == "attention_3":
-                s = s * w[pre + "temp"][hh]
-            if kind == "attention_2":
-                z = torch.cat([s, w[pre + "sink"][hh].reshape(1).to(s.dtype)])
-                p = torch.softmax(z, 0)[:-1]
-            else:
-                p = torch.softmax(s, 0)
-            out[i, hh] = (p[:, None] * vals[jt, g]).sum(0)
+    out = attend(q, kv[0], kv[1], m["scale"], mask.get("size"), int(mask.get("keep_first", 0)),
+                 sink=w[pre + "sink"] if kind == "attention_2" else None,
+                 r1=w[pre + "r1"] if kind == "attention" else None, r2=w[pre + "r2"] if kind == "attention" else None,
+                 temp=w[pre + "temp"] if kind == "attention_3" else None)
     if kind == "attention_2":
         out = out * torch.sigmoid(h @ w[pre + "g"].T)[:, :, None]
     return out.reshape(T, H * vd) @ w[pre + "o"].T
@@ -164,3 +174,71 @@ def forward(cfg, w, tokens, dtype=torch.float32, return_layers=False):
         layers.append(x)
     logits = layer_norm(x, w["final.norm"], w["final.norm.b"], eps) @ w["head"].T
     return (logits, layers) if return_layers else logits
+
+
+def tensor_shapes(cfg):
+    """name -> shape of every checkpoint tensor the config implies."""
+    D, V = int(cfg["width"]), int(cfg["vocab"])
+    out = {"embed": (V, D), "final.norm": (D,), "final.norm.b": (D,), "head": (V, D)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, kind = f"l{i}.", layer["mixer"], layer["type"]
+        H, G, dim, vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        for n in ("norm1", "norm1.b", "norm2", "norm2.b", "shift"):
+            out[p + n] = (D,)
+        out[p + "mix.q"] = (H * dim, D)
+        if "kv_from" not in m:
+            out[p + "mix.k"], out[p + "mix.v"] = (G * dim, D), (G * vd, D)
+        if kind == "attention":
+            out[p + "mix.q.b"] = (H * dim,)
+            if "kv_from" not in m:
+                out[p + "mix.k.b"], out[p + "mix.v.b"] = (G * dim,), (G * vd,)
+            out[p + "mix.r1"], out[p + "mix.r2"] = (H,), (H,)
+        if kind == "attention_2":
+            out[p + "mix.sink"], out[p + "mix.g"] = (H,), (H, D)
+        if kind == "attention_3":
+            out[p + "mix.temp"] = (H,)
+        out[p + "mix.o"] = (D, H * vd)
+        mlp = layer.get("mlp")
+        if not mlp:
+            continue
+        if mlp.get("kind", "dense") == "dense":
+            F = int(mlp["ff"])
+            out.update({p + "mlp.gate": (F, D), p + "mlp.gate.b": (F,), p + "mlp.up": (F, D), p + "mlp.up.b": (F,), p + "mlp.down": (D, F), p + "mlp.down.b": (D,)})
+        else:
+            F, n = int(mlp["expert"]["ff"]), int(mlp["router"]["experts"])
+            for e in range(n):
+                out.update({f"{p}mlp.e{e}.gate": (F, D), f"{p}mlp.e{e}.up": (F, D), f"{p}mlp.e{e}.down": (D, F)})
+            out[p + "mlp.router"], out[p + "mlp.router.b"] = (n, D), (n,)
+            if mlp.get("shared"):
+                Fs = int(mlp["shared"]["ff"])
+                out.update({p + "mlp.shared.gate": (Fs, D), p + "mlp.shared.up": (Fs, D), p + "mlp.shared.down": (D, Fs), p + "mlp.shared.sg": (1, D)})
+    return out
+
+
+def random_weights(cfg, seed=0):
+    """bf16-representable fp32 tensors: projections ~ 1/sqrt(fan-in), norm weights around one, biases and per-head numbers of a size
+    that matters (a dropped bias, sink, penalty or temperature moves the logits far beyond rounding)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        r = torch.randn(shape, generator=g)
+        if name.endswith(("norm1", "norm2", "final.norm")):
+            t = 1.0 + 0.3 * r
+        elif name.endswith("shift"):
+            t = torch.rand(shape, generator=g)
+        elif name.endswith(".b"):
+            t = 0.5 * r
+        elif name.endswith(("r1", "r2")):
+            t = 0.2 + torch.rand(shape, generator=g)
+        elif name.endswith("temp"):
+            t = 0.5 + torch.rand(shape, generator=g)
+        elif name.endswith("sink"):
+            t = r
+        elif name == "embed":
+            t = r
+        elif name.endswith("router"):
+            t = 3.0 * r / math.sqrt(shape[-1])
+        else:
+            t = r / math.sqrt(shape[-1])
+        out[name] = t.to(torch.bfloat16).to(torch.float32)
+    return out
