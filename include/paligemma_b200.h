@@ -82,6 +82,10 @@ int pg_gemm_bf16(const void* x, long long ldx, const void* w, long long ldw, voi
  *  - out_row_map (token-major kernels, PG_EPI_F32 without resid): token t is written to output row out_row_map[t] -- the
  *    multimodal projector (modeling_paligemma.py:57-65) scattering its rows, times `scale`, straight to the `<image>` positions of
  *    the merged embedding sequence (masked_scatter of _merge_input_ids_with_image_features, :201-251); map from pg_merge_scan.
+ *  - PG_EPI_GEGLU takes the kind of gated unit from act_gelu: 0 / 1 gelu_tanh(g) * u, 3 silu(g) * u, 4 the clamped form
+ *    g' = min(g, c), u' = clamp(u, -c, c), g' * sigmoid(glu_alpha * g') * (u' + 1) with c = `scale` (glu_alpha 0 reads as 1).  In this
+ *    mode `bias` (fp32 [features]) is in the packed row order of the weight ([64 gate | 64 up] per 128 rows) and is added before
+ *    the gated unit.
  */
 typedef struct PgGemmFusion {
   float* zero_buf;
@@ -91,6 +95,7 @@ typedef struct PgGemmFusion {
   float stat_c;
   int resid_row_mod;
   const int* out_row_map;
+  float glu_alpha;
 } PgGemmFusion;
 int pg_gemm_bf16_fused(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo,
                        const float* bias, const float* resid, long long ldr, int tokens, int features, int K, int mode,
@@ -478,7 +483,7 @@ int pg_moe_gather_rows(const void* x, long long ldx, const int* sorted_pair, con
  * mid[rows, F] = relu(xg W_up[e]^T)^2 in bf16, eo[rows, D] = mid W_down[e]^T in fp32, both through pg_gemm_bf16.  bf16 only;
  * D, F and the pitches multiples of 8. */
 int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up, const void* w_down, void* mid, long long ldm, float* eo, long long ldo,
-                      const int* counts_host, int n_real, int D, int F, void* stream);
+                      const int* counts_host, int n_real, int D, int F, int glu, void* stream);
 int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,
                    long long ldh, const float* shared_out, long long lds, float* y, int tokens, int D, int top, int act_f32,
                    const float* shared_gate, long long ldsg, int accumulate, void* stream);

@@ -90,7 +90,7 @@ SIGNATURES = {
     "pg_moe_plan": [p, p, p, p, p, p, p, i32, i32, i32, p],
     "pg_moe_gemm": [p, i64, p, i32, p, i64, i64, p, i64, p, i32, i32, i32, i32, i32, i32, i64, i64, p],
     "pg_moe_gather_rows": [p, i64, p, p, i32, p, i64, i32, i32, i32, p],
-    "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, p],
+    "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
     "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p, i64, i32, p],
     "pg_gemm_simt_bias": [p, i64, p, i64, p, i64, p, i32, i32, i32, i32, i32, i32, p],
     "pg_layernorm_shift": [p, p, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],
@@ -109,7 +109,7 @@ class GemmFusion(C.Structure):
     """Mirror of PgGemmFusion (include/paligemma_b200.h)."""
     _fields_ = [
         ("zero_buf", p), ("zero_count", i64),
-        ("stats", p), ("stats_ld", i64), ("stat_c", f32), ("resid_row_mod", i32), ("out_row_map", p),
+        ("stats", p), ("stats_ld", i64), ("stat_c", f32), ("resid_row_mod", i32), ("out_row_map", p), ("glu_alpha", f32),
     ]
 
 
@@ -164,8 +164,11 @@ def require_device():
 # ------------------------------------------------------------------------------------------------------------------
 # thin typed wrappers (argument checking that needs tensor metadata lives here; kernels check the rest)
 # ------------------------------------------------------------------------------------------------------------------
+GLU_GELU, GLU_SILU, GLU_CLAMPED = 1, 3, 4  # gated units of the EPI_GEGLU epilogue (passed as act_gelu)
+
+
 def gemm(x, w, out, *, mode, bias=None, resid=None, act_gelu=0, scale=1.0, swap=-1, split_k=1, features=None, resid_row_mod=0,
-         out_row_map=None):
+         out_row_map=None, glu_alpha=0.0):
     """out[t,f] (mode-dependent) from x [T,K] bf16 and w [F,K] bf16 (nn.Linear layout).  resid_row_mod = N > 0: `resid` is an
     [N, F] table and token t takes row t % N (position embeddings).  out_row_map int32 [T]: token t goes to row out_row_map[t]
     of `out` (projector rows scattered to their `<image>` positions)."""
@@ -177,8 +180,9 @@ def gemm(x, w, out, *, mode, bias=None, resid=None, act_gelu=0, scale=1.0, swap=
         assert bias.dtype == torch.float32 and bias.is_contiguous()
     if resid is not None:
         assert resid.dtype == torch.float32 and resid.stride(-1) == 1
-    if resid_row_mod or out_row_map is not None:
+    if resid_row_mod or out_row_map is not None or glu_alpha:
         fu = GemmFusion()
+        fu.glu_alpha = float(glu_alpha)
         if resid_row_mod:
             assert resid is not None and resid.shape[0] >= resid_row_mod
             fu.resid_row_mod = int(resid_row_mod)

@@ -459,3 +459,194 @@ def run_pukerax(args):
             out[key] = round(out[key], 1)
     print(json.dumps(out), flush=True)
     return out
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# `bench.py --arch kovusun`: the Kovusun decoder beside the Mapedra decoder with softmax attention on every layer (the closest model
+# of the package: same engine, grouped-query softmax attention over pages, gated feed-forward) at equal width / heads / k/v heads /
+# feed-forward / depth; the routed experts beside the grouped kernel as Pukerax's squared-relu experts use it
+# ----------------------------------------------------------------------------------------------------------------------
+def kovusun_config(width, heads, kv_heads, dim, ff, vocab, layers, experts=14, top=4):
+    """Layer types in turn: sink + gate attention (window 1024), rotated attention with kept first tokens (window 2048), biased
+    attention with the distance penalty (window 512), and a layer that borrows the previous layer's keys / values (window 256).
+    The first layer's feed-forward is dense (clamped gated unit), the others routed (expert width ff / 8, shared expert ff / 4)."""
+    base = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5}
+    ls = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0} if i == 0 else {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 4},
+                                                                        "router": {"experts": experts, "top": top}}
+        k = i % 4
+        if k == 0:
+            ls.append({"type": "attention_2", "mixer": dict(base, mask={"size": 1024}), "mlp": mlp})
+        elif k == 1:
+            ls.append({"type": "attention_3", "mixer": dict(base, mask={"size": 2048, "keep_first": 4}, rot={"base": 1e6, "dims": dim}), "mlp": mlp})
+        elif k == 2:
+            ls.append({"type": "attention", "mixer": dict(base, mask={"size": 512}), "mlp": mlp})
+        else:
+            ls.append({"type": "attention", "mixer": dict(base, mask={"size": 256}, kv_from=i - 1), "mlp": mlp})
+    return {"architecture": "Kovusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ls}
+
+
+def random_kovusun(cfg, seed=0):
+    from .modeling_kovusun import KovusunConfig, KovusunForCausalLM
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    c = KovusunConfig(cfg)
+    model = KovusunForCausalLM(c, torch.bfloat16)
+
+    def take(name, shape):
+        r = torch.randn(*shape, device="cuda", generator=g)
+        if name.endswith(("norm1", "norm2", "final.norm")):
+            t = 1.0 + 0.05 * r
+        elif name.endswith("shift"):
+            t = torch.rand(*shape, device="cuda", generator=g)
+        elif name.endswith((".b", "sink")):
+            t = 0.1 * r
+        elif name.endswith(("r1", "r2", "temp")):
+            t = 0.5 + torch.rand(*shape, device="cuda", generator=g)
+        else:
+            t = r * shape[-1] ** -0.5
+        return t.to(torch.bfloat16)
+
+    model.embed = take("embed", (c.vocab, c.width))
+    for blk in model.blocks:
+        blk.load(take, lambda name: name.endswith("shift"))
+    model.final_norm, model.final_norm_b = take("final.norm", (c.width,)), take("final.norm.b", (c.width,))
+    model.head = take("head", (c.vocab, c.width))
+    model.pack()
+    return model
+
+
+def run_kovusun(args):
+    _lib.require_device()
+    torch.cuda.set_device(0)
+    hbm, tflops, src = peaks()
+    W, H, G, dh, F, V, L = args.width, args.heads, args.kv_heads, args.head_dim, args.ff, args.vocab, args.layers
+    B_pre, S, B_dec, ctx = args.prefill_batch, args.seq_len, args.decode_batch, args.context
+    flush = torch.zeros(64 * 1024 * 1024, device="cuda", dtype=torch.float32)  # 256 MB > L2
+    cfg = kovusun_config(W, H, G, dh, F, V, L)
+    out = {"metric": "kovusun_vs_mapedra_tokens_per_s", "dtype": "bf16", "data": "synthetic", "peaks": src,
+           "config": {"width": W, "heads": H, "kv_heads": G, "head_dim": dh, "ff": F, "vocab": V, "layers": L,
+                      "windows": [l["mixer"]["mask"] for l in cfg["layers"][:4]], "router": cfg["layers"][-1]["mlp"].get("router") if L > 1 else None,
+                      "prefill": [B_pre, S], "decode": [B_dec, ctx], "l2": "256 MB buffer rewritten before every timed launch"}}
+    model = random_kovusun(cfg)
+    eng = _throughput(model, args, flush, V, "kovusun", out)
+
+    # ---------------------------------------------------------------- Kovusun kernels
+    prec, k, store = model.prec, {}, eng.store
+    ff = next((b.ff for b in model.blocks if hasattr(b.ff, "n_real")), None)
+    blk0 = model.blocks[0]
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        x, a1, a2 = torch.randn(T, W, device="cuda"), prec.empty(T, W), prec.empty(T, W)
+        k[f"two_norms_shift_{name}"] = dict(
+            s=timed(lambda: seq_ops.layernorm_shift(x, blk0.norm1_d, blk0.norm1_bd, a1, 1e-5, shift=blk0.shift_d, state=store.state[L], b=b, w2=blk0.norm2_d,
+                                                    b2=blk0.norm2_bd, out2=a2), flush=flush), bytes=T * W * (4 + 2 + 2))
+        for li, blk in enumerate(model.blocks[:4]):
+            mx = blk.mixer
+            tag = cfg["layers"][li]["type"] + ("_borrowed" if mx.kv_from is not None else "")
+            src_li = li if mx.kv_from is None else mx.kv_from
+            kp, vp = store.k_pages[src_li], store.v_pages[src_li]
+            kp.normal_()
+            vp.normal_()
+            proj = torch.randn(T, mx.w_in.shape[0], device="cuda").to(torch.bfloat16)
+            q, o = prec.empty(T, H * dh), prec.empty(T, H * dh)
+            own = mx.kv_from is None
+            k[f"attn_prepare_{tag}_{name}"] = dict(
+                s=timed(lambda: seq_ops.attn_prepare(proj, b, mx.freq_d, None, None, q, kp if own else None, vp if own else None, H, G, dh, dh, mx.rot_dims, 1e-5,
+                                                     PAGE, norm_qk=mx.qk_norm, norm_v=False), flush=flush), bytes=T * (H + (2 * G if own else 0)) * dh * 2 * 2)
+            win, keep = mx.window, mx.keep_first
+            # (query, key) pairs inside the window (+ kept first keys) and the key rows a sequence's queries read
+            if n_new > 1:
+                pairs = n_seq * sum(min(i + 1, win) + max(0, min(keep, i + 1 - win)) for i in range(c0, c0 + n_new))
+                keys_read = c0 + n_new
+            else:
+                pairs = n_seq * min(c0 + 1, win + keep)
+                keys_read = min(c0 + 1, win + keep)
+            gate = proj[:, mx.gate_col:] if mx.head_gate else None
+            k[f"attention_{tag}_{name}"] = dict(
+                s=timed(lambda: seq_ops.attn_ragged(q, kp, vp, gate, o, b, H, G, dh, dh, mx.scale, 0.0, PAGE, gate_per_head=True, score=mx.score), flush=flush),
+                flops=4 * dh * H * pairs, bytes=n_seq * keys_read * G * 2 * dh * 2 + 2 * T * H * dh * 2)
+        if ff is not None:
+            h = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+            z = torch.randn(T, ff.w_router.shape[0], device="cuda")
+
+            def route():
+                ids, wts, counts = seq_ops.moe_route(z[:, :ff.n_all], None, ff.n_real, ff.top, 1, 1, 1.0, logit_bias=ff.router_b)
+                return ids, wts, counts, seq_ops.MoePlan(ids, counts, ff.n_real)
+
+            k[f"moe_route_plan_{name}"] = dict(s=timed(lambda: route(), flush=flush), bytes=T * (ff.n_all * 4 + ff.top * 16))
+            ids, wts, counts, plan = route()
+            wbytes = 3 * ff.n_real * ff.F * W * 2
+            k[f"moe_expert_products_{name}"] = dict(s=timed(lambda: ff.expert_products(h, plan, counts, prec), flush=flush), flops=6 * plan.pairs * ff.F * W,
+                                                    bytes=wbytes + plan.pairs * (W * 2 + ff.F * 4 + W * 4))
+            # the same grouped kernel as squared-relu experts use it (one up projection of the same total width: 2 F rows)
+            mid2 = prec.empty(plan.pairs, 2 * ff.F)
+            eo2 = torch.empty(plan.pairs, W, device="cuda", dtype=torch.float32)
+            w_dn2 = torch.randn(ff.n_real, W, 2 * ff.F, device="cuda").to(torch.bfloat16)
+            k[f"moe_relu2_same_kernel_{name}"] = dict(
+                s=timed(lambda: (seq_ops.moe_gemm(h, plan, ff.w_up, mid2, gather=True, act=seq_ops.ACT_RELU2), seq_ops.moe_gemm(mid2, plan, w_dn2, eo2, gather=False)),
+                        flush=flush), flops=8 * plan.pairs * ff.F * W, bytes=4 * ff.n_real * ff.F * W * 2 + plan.pairs * (W * 2 + ff.F * 8 + W * 4))
+            eo = ff.expert_products(h, plan, counts, prec)
+            sh, xr = torch.randn(T, W, device="cuda"), torch.randn(T, W, device="cuda")
+            k[f"moe_combine_residual_{name}"] = dict(
+                s=timed(lambda: seq_ops.moe_combine(eo, plan, ids, wts, h, sh, xr, shared_gate=z[:, ff.n_all:ff.n_all + 1], accumulate=True), flush=flush),
+                bytes=T * W * (ff.top * 4 + 4 + 4 + 4))
+        dense_ff = blk0.ff
+        if dense_ff is not None and hasattr(dense_ff, "limit"):
+            h = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+            xr = torch.randn(T, W, device="cuda")
+            k[f"clamped_glu_feed_forward_{name}"] = dict(s=timed(lambda: dense_ff(h, b, prec, resid=xr), flush=flush), flops=6 * T * W * dense_ff.F,
+                                                         bytes=3 * W * dense_ff.F * 2 + T * (W * 2 + dense_ff.F * 4 + W * 8))
+        for i in range(n_seq):
+            store.release(("k", i))
+    del eng, model, store
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- Mapedra (softmax attention on every layer) at equal size
+    mc = mapedra_config(W, H, G, dh, F, V, L, every=1)
+    mm = random_mapedra(mc)
+    eng = _throughput(mm, args, flush, V, "mapedra", out)
+    store, prec = eng.store, mm.prec
+    att_m = mm.blocks[0].mixer
+    ffm = mm.blocks[0].ff
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        proj = torch.randn(T, att_m.w_in.shape[0], device="cuda").to(torch.bfloat16)
+        q, o = prec.empty(T, H * dh), prec.empty(T, H * dh)
+        kp, vp = store.k_pages[0], store.v_pages[0]
+        kp.normal_()
+        vp.normal_()
+        gate = proj[:, (H + G) * dh + G * dh:]
+        k[f"mapedra_attn_prepare_{name}"] = dict(
+            s=timed(lambda: seq_ops.attn_prepare(proj, b, att_m.freq_d, att_m.qn, att_m.kn, q, kp, vp, H, G, dh, dh, att_m.rot_dims, 1e-6, PAGE), flush=flush),
+            bytes=T * (H + 2 * G) * dh * 2 * 2)
+        pairs = n_seq * (n_new * c0 + n_new * (n_new + 1) // 2)
+        k[f"mapedra_attention_{name}"] = dict(
+            s=timed(lambda: seq_ops.attn_ragged(q, kp, vp, gate, o, b, H, G, dh, dh, att_m.scale, att_m.softcap, PAGE), flush=flush),
+            flops=4 * dh * H * pairs, bytes=n_seq * (c0 + n_new) * G * 2 * dh * 2 + 3 * T * H * dh * 2)
+        y, x, xa = torch.randn(T, W, device="cuda"), torch.randn(T, W, device="cuda"), prec.empty(T, W)
+        w1 = torch.ones(W, device="cuda")
+        k[f"mapedra_group_norm_residual_{name}"] = dict(s=timed(lambda: seq_ops.group_rmsnorm_add(y, w1, x, xa, 4, 1e-6), flush=flush), bytes=T * W * (4 + 4 + 4 + 2))
+        h = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+        k[f"mapedra_geglu_feed_forward_{name}"] = dict(s=timed(lambda: ffm(h, b, prec), flush=flush), flops=6 * T * W * ffm.F,
+                                                       bytes=3 * W * ffm.F * 2 + T * (W * 2 + ffm.F * 4 + W * 4))
+        for i in range(n_seq):
+            store.release(("k", i))
+    for name, d in k.items():
+        d["us"] = round(d.pop("s") * 1e6, 2)
+        if "bytes" in d:
+            d["hbm_frac"] = round(d["bytes"] / (d["us"] * 1e-6) / hbm, 4)
+        if "flops" in d:
+            d["tflops"] = round(d["flops"] / (d["us"] * 1e-6) / 1e12, 2)
+            d["tensor_frac"] = round(d["flops"] / (d["us"] * 1e-6) / tflops, 5)
+    out["kernels"] = k
+    out["value"] = out["kovusun_decode_tok_s"]
+    out["unit"] = "tokens/s"
+    out["n_gpus"] = 1
+    for key in list(out):
+        if key.endswith("tok_s"):
+            out[key] = round(out[key], 1)
+    print(json.dumps(out), flush=True)
+    return out

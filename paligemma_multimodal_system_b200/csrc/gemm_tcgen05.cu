@@ -52,6 +52,7 @@ struct GemmArgs {
   int split_k;
   int mode, act_gelu;
   float scale;
+  float glu_alpha;  // GEGLU mode, gated-unit kind 4: the sigmoid's slope
   void* out;
   long long ldo;
   const float* bias;
@@ -132,6 +133,18 @@ PG_DEVINL TileInfo decode_tile(int tile, int m_blocks, int n_blocks, int total_k
 PG_DEVINL float epilogue_act(float x, int act) {
   if (act == 2) { const float r = fmaxf(x, 0.f); return r * r; }
   return gelu_tanh_fast(x);
+}
+
+// gated unit of the GEGLU epilogue (GemmArgs::act_gelu in that mode): 0 / 1 gelu_tanh(g) * u; 3 silu(g) * u;
+// 4 clamped: g' = min(g, c), u' = clamp(u, -c, c), g' * sigmoid(alpha * g') * (u' + 1) with c = GemmArgs::scale
+PG_DEVINL float glu_act(float g, float u, int kind, float limit, float alpha) {
+  if (kind == 3) return g / (1.0f + __expf(-g)) * u;
+  if (kind == 4) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+  }
+  return gelu_tanh_fast(g) * u;
 }
 
 PG_DEVINL void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
@@ -593,6 +606,10 @@ PG_DEVINL void geglu_swap_epilogue_group(const GemmArgs& args, uint32_t taddr, f
   __nv_bfloat16* out_bf = reinterpret_cast<__nv_bfloat16*>(args.out);
   const bool is_gate = q < 2;
   const int r = (q * 32 + lane) & 63;
+  const int kind = args.act_gelu;
+  const float glim = args.scale, galpha = args.glu_alpha;
+  // bias of this thread's packed weight row (rows of a 128-row tile: [64 gate | 64 up]); it travels with the exchanged value
+  const float bias_me = args.bias != nullptr ? __ldg(args.bias + m_blk * 128 + q * 32 + lane) : 0.f;
   float* xsend = xg + (is_gate ? 64 * HB : 0);  // gate warps fill the second half of the area, up warps the first
   float* xrecv = xg + (is_gate ? 0 : 64 * HB);
   const int send0 = is_gate ? HB : 0, keep0 = is_gate ? 0 : HB;
@@ -603,7 +620,7 @@ PG_DEVINL void geglu_swap_epilogue_group(const GemmArgs& args, uint32_t taddr, f
     if constexpr (LDN == 16) tmem_ld16(taddr + send0 + c0, v); else tmem_ld8(taddr + send0 + c0, v);
     tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < LDN; ++i) xsend[r * HB + ((c0 + i) ^ (r & (HB - 1) & 31))] = __uint_as_float(v[i]);
+    for (int i = 0; i < LDN; ++i) xsend[r * HB + ((c0 + i) ^ (r & (HB - 1) & 31))] = __uint_as_float(v[i]) + bias_me;
   }
   named_bar_sync(bar, 128);
   uint32_t pk[HB / 2];
@@ -619,9 +636,9 @@ PG_DEVINL void geglu_swap_epilogue_group(const GemmArgs& args, uint32_t taddr, f
       float res[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        float mine = __uint_as_float(v[i + e]);
+        float mine = __uint_as_float(v[i + e]) + bias_me;
         float other = xrecv[r * HB + ((c0 + i + e) ^ (r & (HB - 1) & 31))];
-        res[e] = is_gate ? gelu_tanh_fast(mine) * other : gelu_tanh_fast(other) * mine;
+        res[e] = is_gate ? glu_act(mine, other, kind, glim, galpha) : glu_act(other, mine, kind, glim, galpha);
       }
       pk[(c0 + i) / 2] = pack_bf16(res[0], res[1]);
     }
@@ -691,10 +708,16 @@ PG_DEVINL void token_major_epilogue(const GemmArgs& args, uint32_t taddr, int m_
         tmem_ld16(taddr + blk * 128 + c0, g);
         tmem_ld16(taddr + blk * 128 + 64 + c0, u);
         tmem_ld_wait();
+        const float* bg = args.bias != nullptr ? args.bias + n_blk * BN + blk * 128 + c0 : nullptr;  // packed order: [64 gate | 64 up]
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float a = gelu_tanh_fast(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
-          float b = gelu_tanh_fast(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
+          float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]), u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+          if (bg != nullptr) {
+            g0 += __ldg(bg + 2 * i); g1 += __ldg(bg + 2 * i + 1);
+            u0 += __ldg(bg + 64 + 2 * i); u1 += __ldg(bg + 64 + 2 * i + 1);
+          }
+          float a = glu_act(g0, u0, args.act_gelu, args.scale, args.glu_alpha);
+          float b = glu_act(g1, u1, args.act_gelu, args.scale, args.glu_alpha);
           pk[(c0 / 2 + i) & 31] = pack_bf16(a, b);
         }
       }
@@ -1176,6 +1199,8 @@ extern "C" int pg_gemm_bf16_fused(const void* x, long long ldx, const void* w, l
   GemmArgs a = {};
   a.tokens = tokens; a.features = features; a.K = K; a.split_k = split_k; a.mode = mode; a.act_gelu = act_gelu;
   a.scale = scale; a.out = out; a.ldo = ldo; a.bias = bias; a.resid = resid; a.ldr = ldr;
+  a.glu_alpha = (fu != nullptr && fu->glu_alpha != 0.f) ? fu->glu_alpha : 1.0f;
+  if (mode == PG_EPI_GEGLU && act_gelu != 0 && act_gelu != 1 && act_gelu != 3 && act_gelu != 4) return PG_ERR_ARG;
   if (fu != nullptr && fu->resid_row_mod > 0) {
     if (swap || resid == nullptr || mode != PG_EPI_F32) return PG_ERR_ARG;  // a token-major fp32 epilogue feature
     a.resid_mod = fu->resid_row_mod;

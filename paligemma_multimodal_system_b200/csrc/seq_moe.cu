@@ -533,8 +533,9 @@ SideStreams* side_streams() {
 }  // namespace
 
 extern "C" int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up, const void* w_down, void* mid, long long ldm, float* eo, long long ldo,
-                                 const int* counts_host, int n_real, int D, int F, void* stream) {
-  if (n_real <= 0 || D <= 0 || F <= 0 || counts_host == nullptr) return PG_ERR_ARG;
+                                 const int* counts_host, int n_real, int D, int F, int glu, void* stream) {
+  if (n_real <= 0 || D <= 0 || F <= 0 || counts_host == nullptr || (glu && (F % 64) != 0)) return PG_ERR_ARG;
+  const int up_rows = glu ? 2 * F : F;  // gated experts: [64 gate | 64 up] packed rows, the gated unit in the product's epilogue
   const bf16* x = static_cast<const bf16*>(xg);
   const bf16* wu = static_cast<const bf16*>(w_up);
   const bf16* wd = static_cast<const bf16*>(w_down);
@@ -555,7 +556,8 @@ extern "C" int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up
     if (c <= 0) continue;
     void* st = ss != nullptr ? static_cast<void*>(ss->s[used++ % kSideStreams]) : stream;
     const int swap = c <= 128 ? 1 : 0;
-    rc = pg_gemm_bf16(x + off * ldx, ldx, wu + (long long)e * F * D, D, m + off * ldm, ldm, nullptr, nullptr, 0, c, F, D, PG_EPI_BF16, 2, 1.0f, swap, 1, st);
+    rc = pg_gemm_bf16(x + off * ldx, ldx, wu + (long long)e * up_rows * D, D, m + off * ldm, ldm, nullptr, nullptr, 0, c, up_rows, D,
+                      glu ? PG_EPI_GEGLU : PG_EPI_BF16, glu ? 3 : 2, 1.0f, swap, 1, st);
     if (rc == PG_OK)
       rc = pg_gemm_bf16(m + off * ldm, ldm, wd + (long long)e * D * F, F, eo + off * ldo, ldo, nullptr, nullptr, 0, c, D, F, PG_EPI_F32, 0, 1.0f, swap, 1, st);
     off += c;

@@ -254,17 +254,42 @@ class GluFeedForward:
             self.w.update(gate_b=take(pre + "gate.b", (F,)), up_b=take(pre + "up.b", (F,)), down_b=take(pre + "down.b", (D,)))
 
     def pack(self, prec):
-        w = self.w
+        w, F, D = self.w, self.F, self.D
         f32 = dict(device="cuda", dtype=torch.float32)
-        self.w_gu = torch.cat([w["gate"], w["up"]], 0).to("cuda", prec.dtype).contiguous()
-        self.w_down = w["down"].to("cuda", prec.dtype).contiguous()
-        self.b_gu = torch.cat([w["gate_b"], w["up_b"]]).to(**f32).contiguous() if self.bias else None
         self.b_down = w["down_b"].to(**f32).contiguous() if self.bias else None
+        # bf16: the tcgen05 GEMM computes the gated unit (and adds the biases) in its epilogue from a [64 gate | 64 up] row-interleaved
+        # weight; F is padded to a multiple of 64 with zero rows (both forms map (0, 0) to 0) and zero columns of the down projection
+        self.fused = prec.dtype == torch.bfloat16 and D % 8 == 0
+        if self.fused:
+            Fp = (F + 63) // 64 * 64
+            gate = torch.zeros(Fp, D, device="cuda", dtype=torch.bfloat16)
+            up = torch.zeros_like(gate)
+            gate[:F], up[:F] = w["gate"].to("cuda", torch.bfloat16), w["up"].to("cuda", torch.bfloat16)
+            self.w_gu = torch.empty(2 * Fp, D, device="cuda", dtype=torch.bfloat16)
+            _lib.check(_lib.lib().pg_pack_gate_up(gate.data_ptr(), up.data_ptr(), self.w_gu.data_ptr(), Fp, D, _lib.stream()), "pg_pack_gate_up")
+            self.w_down = torch.zeros(D, Fp, device="cuda", dtype=torch.bfloat16)
+            self.w_down[:, :F] = w["down"].to("cuda", torch.bfloat16)
+            self.b_gu = None
+            if self.bias:
+                bg, bu = torch.zeros(Fp, **f32), torch.zeros(Fp, **f32)
+                bg[:F], bu[:F] = w["gate_b"].to(**f32), w["up_b"].to(**f32)
+                self.b_gu = torch.stack([bg.view(-1, 64), bu.view(-1, 64)], 1).reshape(-1).contiguous()  # the weight's packed row order
+            self.Fp = Fp
+            torch.cuda.synchronize()
+        else:
+            self.w_gu = torch.cat([w["gate"], w["up"]], 0).to("cuda", prec.dtype).contiguous()
+            self.w_down = w["down"].to("cuda", prec.dtype).contiguous()
+            self.b_gu = torch.cat([w["gate_b"], w["up_b"]]).to(**f32).contiguous() if self.bias else None
 
     def __call__(self, h, b, prec, resid=None):
         T = h.shape[0]
-        gu = seq_ops.linear(h, self.w_gu, prec.empty(T, 2 * self.F), bias=self.b_gu)
-        mid = seq_ops.glu(gu, prec.empty(T, self.F), self.kind, self.limit, self.alpha)
+        if self.fused:
+            mid = prec.empty(T, self.Fp)
+            _lib.gemm(h, self.w_gu, mid, mode=_lib.EPI_GEGLU, act_gelu=_lib.GLU_CLAMPED if self.kind == seq_ops.GLU_CLAMPED else _lib.GLU_SILU,
+                      scale=self.limit, glu_alpha=self.alpha, bias=self.b_gu, swap=1 if T <= 128 else 0)
+        else:
+            gu = seq_ops.linear(h, self.w_gu, prec.empty(T, 2 * self.F), bias=self.b_gu)
+            mid = seq_ops.glu(gu, prec.empty(T, self.F), self.kind, self.limit, self.alpha)
         if resid is not None:
             return seq_ops.linear_add(mid, self.w_down, resid, bias=self.b_down)
         return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32), bias=self.b_down)
@@ -443,6 +468,12 @@ class RoutedFeedForward:
                 # rows alternate gate / up: an accumulator pair of the grouped product's epilogue is one output feature
                 gu = torch.stack([torch.stack(w["gate"]), torch.stack(w["up"])], 2)  # [n, F, 2, D]
                 self.w_up = gu.reshape(self.n_real, 2 * self.F, self.D).to("cuda", prec.dtype).contiguous()
+                self.w_up_dense = None
+                if prec.dtype == torch.bfloat16 and self.F % 64 == 0 and self.D % 8 == 0:
+                    # second copy for the per-expert dense products of long prompt portions: [64 gate | 64 up] row blocks, the order
+                    # the tcgen05 product's gated epilogue reads
+                    blk = torch.stack([torch.stack(w["gate"]).view(self.n_real, -1, 64, self.D), torch.stack(w["up"]).view(self.n_real, -1, 64, self.D)], 2)
+                    self.w_up_dense = blk.reshape(self.n_real, 2 * self.F, self.D).to("cuda", prec.dtype).contiguous()
             else:
                 self.w_up = torch.stack(w["up"]).to("cuda", prec.dtype).contiguous()
             self.w_down = torch.stack(w["down"]).to("cuda", prec.dtype).contiguous()
@@ -453,7 +484,7 @@ class RoutedFeedForward:
     DENSE_SEGMENT_ROWS = 256
 
     def _dense_segments(self, T, prec):
-        return (not self.glu and not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
+        return ((not self.glu or self.w_up_dense is not None) and not prec.f32 and self.D % 8 == 0 and self.F % 8 == 0 and T * self.top >= self.DENSE_SEGMENT_ROWS * self.n_real
                 and not torch.cuda.is_current_stream_capturing())
 
     def expert_products(self, h, plan, counts, prec):
@@ -466,8 +497,9 @@ class RoutedFeedForward:
             xg = seq_ops.moe_gather_rows(h, plan, prec.empty(plan.pairs, self.D))
             mid = prec.empty(plan.pairs, self.F)
             eo = torch.empty(plan.pairs, self.D, device="cuda", dtype=torch.float32)
-            _lib.check(_lib.lib().pg_moe_dense_runs(xg.data_ptr(), xg.stride(0), self.w_up.data_ptr(), self.w_down.data_ptr(), mid.data_ptr(), mid.stride(0),
-                                                    eo.data_ptr(), eo.stride(0), C.addressof(per), self.n_real, self.D, self.F, _lib.stream()),
+            w_up = self.w_up_dense if self.glu else self.w_up
+            _lib.check(_lib.lib().pg_moe_dense_runs(xg.data_ptr(), xg.stride(0), w_up.data_ptr(), self.w_down.data_ptr(), mid.data_ptr(), mid.stride(0),
+                                                    eo.data_ptr(), eo.stride(0), C.addressof(per), self.n_real, self.D, self.F, int(self.glu), _lib.stream()),
                        "pg_moe_dense_runs")
             return eo
         mid = seq_ops.moe_gemm(h, plan, self.w_up, prec.empty(plan.pairs, self.F), gather=True, act=seq_ops.ACT_SILU_GLU if self.glu else seq_ops.ACT_RELU2)

@@ -572,3 +572,29 @@ def test_registry_loads_a_checkpoint_folder(tmp_path):
     tk = toks(50, cfg["vocab"], 5)
     eng = SequenceEngine(load_model(str(tmp_path), dtype=torch.float32), 128, 1)
     assert rel_err(eng.step([("a", tk, list(range(50)))], ["a"]), O.forward(cfg, w, tk)) < F32_TOL
+
+
+@pytest.mark.parametrize("T", [40, 300])
+def test_gated_experts_as_dense_runs_per_expert(T, monkeypatch):
+    """Long prompt portions hand every expert's tokens to dense tensor-core products with the gated unit in the epilogue;
+    forced here at a small size and compared with the grouped kernel and the oracle."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    from paligemma_multimodal_system_b200.mixers import RoutedFeedForward
+    from paligemma_multimodal_system_b200.modeling_kovusun import _feed_forward
+    D, mlp = 64, moe(experts=5, top=2, ff=128, shared=0)
+    cfg = make_cfg([{"type": "attention_2", "mixer": mixer("attention_2"), "mlp": mlp}], width=D)
+    w = O.random_weights(cfg, seed=T)
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).float()
+    ref = O.feed_forward(h, w, "l0.mlp.", mlp)
+    ff = _feed_forward(D, mlp)
+    left = {k: v.to(torch.bfloat16) for k, v in w.items()}
+    ff.load(lambda name, shape: left.pop(name), "l0.mlp.")
+    prec = seq_ops.Precision(torch.bfloat16)
+    ff.pack(prec)
+    assert ff.w_up_dense is not None
+    hd = h.cuda().to(torch.bfloat16).contiguous()
+    grouped = ff(hd, None, prec)
+    monkeypatch.setattr(RoutedFeedForward, "DENSE_SEGMENT_ROWS", 1)
+    assert ff._dense_segments(T, prec)
+    dense_runs = ff(hd, None, prec)
+    assert close(dense_runs, ref, torch.bfloat16) and rel_err(dense_runs, grouped.cpu()) < 1e-2
