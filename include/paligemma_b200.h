@@ -481,7 +481,8 @@ int pg_moe_gather_rows(const void* x, long long ldx, const int* sorted_pair, con
                        int max_rows, int D, int act_f32, void* stream);
 /* Per-expert dense products over the gathered runs: expert e owns the next counts_host[e] rows (host array, n_real entries);
  * mid[rows, F] = relu(xg W_up[e]^T)^2 in bf16, eo[rows, D] = mid W_down[e]^T in fp32, both through pg_gemm_bf16.  bf16 only;
- * D, F and the pitches multiples of 8. */
+ * D, F and the pitches multiples of 8.  glu != 0: w_up holds [n_real, 2F, D] with gate and up rows in blocks of 64
+ * ([64 gate | 64 up], F a multiple of 64) and mid = silu(gate) * up comes from the product's gated epilogue. */
 int pg_moe_dense_runs(const void* xg, long long ldx, const void* w_up, const void* w_down, void* mid, long long ldm, float* eo, long long ldo,
                       const int* counts_host, int n_real, int D, int F, int glu, void* stream);
 int pg_moe_combine(const float* expert_out, long long ldy, const int* pair_row, const int* ids, const float* weights, const void* h,

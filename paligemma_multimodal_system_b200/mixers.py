@@ -488,7 +488,7 @@ class RoutedFeedForward:
                 and not torch.cuda.is_current_stream_capturing())
 
     def expert_products(self, h, plan, counts, prec):
-        """fp32 rows [pairs, D] in the plan's sorted order: down(relu(up h)^2) of every (token, real expert) pair."""
+        """fp32 rows [pairs, D] in the plan's sorted order: the expert's output for every (token, real expert) pair."""
         T = h.shape[0]
         if self._dense_segments(T, prec):
             # many rows per expert (prompt portions): the pair counts come to the host once per layer, every expert's tokens are
