@@ -311,6 +311,7 @@ int pg_gemm_simt_batched(const void* x, long long ldx, long long batch_x, const 
                          long long ldo, long long batch_out, int tokens, int features, int K, int batch, int in_f32, int out_f32,
                          void* stream);
 
+/* out[t, 0:D] (fp32) = table[tokens[t], col0 : col0 + D] * scale  (embedding lookup; table bf16 or fp32, pitch ld). */
 int pg_embed_rows(const int* tokens, const void* table, long long ld, int col0, float* out, int rows, int D, float scale,
                   int table_f32, void* stream);
 

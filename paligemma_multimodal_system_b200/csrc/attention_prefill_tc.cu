@@ -143,7 +143,7 @@ PG_DEVINL float exp2_mufu(float x) {
 // the XU pipe too), cubic for 2^f on [-0.5, 0.5] (relative error < 1e-4, more than an order of magnitude below the bf16 rounding of the
 // probability that follows), n added into the exponent field.  x <= 8 by the lazy maximum; x = -inf (masked keys) clamps to
 // 2^-126, which rounds to a bf16 denormal that weighs nothing.
-// (Round 1 measured this as "no gain": at that time the single MMA-issuing thread, not the softmax, paced the kernel.)
+// (An earlier measurement showed "no gain": at that time the single MMA-issuing thread, not the softmax, paced the kernel.)
 PG_DEVINL float exp2_fma(float x) {
   x = fmaxf(x, -126.0f);
   const float t = x + 12582912.0f;

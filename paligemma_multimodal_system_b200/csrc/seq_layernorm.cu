@@ -113,6 +113,133 @@ __global__ void __launch_bounds__(256) layernorm_shift_kernel(const float* __res
   }
 }
 
+// The same for widths that are a multiple of 4 up to 8192: the row (and the row before) in registers as VT float4 per thread, every
+// load of both rows in flight at once, and the two rows' statistics reduced TOGETHER (two block reductions for mean and variance
+// of both rows).  Used whenever the pointers are 16-byte aligned; the kernel above is the fallback for other widths.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float (*red)[8]) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, o);
+    b += __shfl_xor_sync(0xffffffffu, b, o);
+  }
+  __syncthreads();  // the previous use of `red` is over
+  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = a; red[1][threadIdx.x >> 5] = b; }
+  __syncthreads();
+  a = 0.f; b = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { a += red[0][w]; b += red[1][w]; }
+}
+
+__device__ __forceinline__ float sum4(float4 v) { return (v.x + v.y) + (v.z + v.w); }
+__device__ __forceinline__ float dev4(float4 v, float m) {
+  const float a = v.x - m, b = v.y - m, c = v.z - m, d = v.w - m;
+  return fmaf(a, a, fmaf(b, b, fmaf(c, c, d * d)));
+}
+__device__ __forceinline__ float4 ln4(float4 v, float mean, float rstd, float4 w, float4 b) {
+  return make_float4(fmaf((v.x - mean) * rstd, w.x, b.x), fmaf((v.y - mean) * rstd, w.y, b.y), fmaf((v.z - mean) * rstd, w.z, b.z),
+                     fmaf((v.w - mean) * rstd, w.w, b.w));
+}
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TO, int VT>
+__global__ void __launch_bounds__(256) layernorm_shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ b1,
+                                                                  const float* __restrict__ shift, const float* __restrict__ w2,
+                                                                  const float* __restrict__ b2, TO* __restrict__ out1, TO* __restrict__ out2,
+                                                                  float* __restrict__ state, const int* __restrict__ pos,
+                                                                  const int* __restrict__ row_entry, const int* __restrict__ entry_row0,
+                                                                  const int* __restrict__ entry_n, const int* __restrict__ entry_slot, int D, float eps) {
+  __shared__ float red[2][8];
+  const long long t = blockIdx.x;
+  int e = 0, first = 0, n = 1, prev_kind = 0;
+  if (shift != nullptr) {
+    e = row_entry[t];
+    first = entry_row0[e];
+    n = entry_n[e];
+    prev_kind = pos[t] == 0 ? 0 : t == first ? 1 : 2;  // zeros / the state slot / the row before
+  }
+  const bool owner = shift != nullptr && t == first;
+  float* slot = shift != nullptr ? state + (long long)entry_slot[e] * D : nullptr;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v[VT], u[VT];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < VT; ++i) {
+    const int d = 4 * (threadIdx.x + 256 * i);
+    v[i] = d < D ? ld4(x + t * D + d) : zero;
+    u[i] = (prev_kind == 2 && d < D) ? ld4(x + (t - 1) * D + d) : (prev_kind == 1 && d < D) ? ld4(slot + d) : zero;
+    s1 += sum4(v[i]);
+    s2 += sum4(u[i]);
+  }
+  block_sum2(s1, s2, red);
+  const float mean = s1 / (float)D, pm = s2 / (float)D;
+  float q1 = 0.f, q2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < VT; ++i)
+    if (4 * (threadIdx.x + 256 * i) < D) {
+      q1 += dev4(v[i], mean);
+      q2 += dev4(u[i], pm);
+    }
+  block_sum2(q1, q2, red);
+  const float rstd = 1.0f / sqrtf(q1 / (float)D + eps), pr = 1.0f / sqrtf(q2 / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < VT; ++i) {
+    const int d = 4 * (threadIdx.x + 256 * i);
+    if (d >= D) continue;
+    const float4 w = ld4(w1 + d), b = ld4(b1 + d);
+    const float4 a = ln4(v[i], mean, rstd, w, b);
+    if (shift != nullptr) {
+      const float4 ap = prev_kind == 2 ? ln4(u[i], pm, pr, w, b) : u[i];  // the slot already holds a; zeros at position 0
+      const float4 sh = ld4(shift + d);
+      st4(out1 + t * D + d, make_float4(fmaf(ap.x - a.x, sh.x, a.x), fmaf(ap.y - a.y, sh.y, a.y), fmaf(ap.z - a.z, sh.z, a.z), fmaf(ap.w - a.w, sh.w, a.w)));
+      if (owner && n == 1) st4(slot + d, a);  // the same thread read slot[d .. d + 3] above
+    } else {
+      st4(out1 + t * D + d, a);
+    }
+    if (out2 != nullptr) st4(out2 + t * D + d, ln4(v[i], mean, rstd, ld4(w2 + d), ld4(b2 + d)));
+  }
+  if (owner && n > 1) {  // this CTA alone touches the slot: a of the entry's last row
+    const float* xl = x + (long long)(first + n - 1) * D;
+    float sl = 0.f, dummy = 0.f;
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+      const int d = 4 * (threadIdx.x + 256 * i);
+      u[i] = d < D ? ld4(xl + d) : zero;
+      sl += sum4(u[i]);
+    }
+    block_sum2(sl, dummy, red);
+    const float lm = sl / (float)D;
+    float ql = 0.f;
+#pragma unroll
+    for (int i = 0; i < VT; ++i)
+      if (4 * (threadIdx.x + 256 * i) < D) ql += dev4(u[i], lm);
+    block_sum2(ql, dummy, red);
+    const float lr = 1.0f / sqrtf(ql / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+      const int d = 4 * (threadIdx.x + 256 * i);
+      if (d < D) st4(slot + d, ln4(u[i], lm, lr, ld4(w1 + d), ld4(b1 + d)));
+    }
+  }
+}
+
+template <typename TO, int VT>
+int launch_ln_vec(const float* x, const float* w1, const float* b1, const float* shift, const float* w2, const float* b2, void* out1, void* out2, float* state,
+                  const int* pos, const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_slot, int rows, int D, float eps,
+                  cudaStream_t st) {
+  layernorm_shift_vec_kernel<TO, VT><<<rows, 256, 0, st>>>(x, w1, b1, shift, w2, b2, static_cast<TO*>(out1), static_cast<TO*>(out2), state, pos, row_entry,
+                                                           entry_row0, entry_n, entry_slot, D, eps);
+  pg_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+}
+
 // kind 1: silu(g) * u;  kind 2: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)
 template <typename TA>
 __global__ void glu_kernel(const TA* __restrict__ gu, long long ldgu, TA* __restrict__ out, long long ldo, int F, long long total, int kind,
@@ -144,6 +271,17 @@ extern "C" int pg_layernorm_shift(const float* x, const float* w1, const float* 
   const size_t smem = (size_t)(shift != nullptr ? 2 : 1) * D * sizeof(float);
   if (smem > 200 * 1024) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (D % 4 == 0 && D <= 8192 && al16(x) && al16(w1) && al16(b1) && al16(shift) && al16(w2) && al16(b2) && al16(out1) && al16(out2) && al16(state)) {
+#define PG_LNV(VT)                                                                                                                                      \
+  return out_f32 ? launch_ln_vec<float, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, D, eps, st) \
+                 : launch_ln_vec<bf16, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, D, eps, st)
+    if (D <= 1024) PG_LNV(1);
+    if (D <= 2048) PG_LNV(2);
+    if (D <= 4096) PG_LNV(4);
+    PG_LNV(8);
+#undef PG_LNV
+  }
   if (out_f32) {
     auto kern = layernorm_shift_kernel<float>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
