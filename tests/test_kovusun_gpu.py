@@ -598,3 +598,20 @@ def test_gated_experts_as_dense_runs_per_expert(T, monkeypatch):
     assert ff._dense_segments(T, prec)
     dense_runs = ff(hd, None, prec)
     assert close(dense_runs, ref, torch.bfloat16) and rel_err(dense_runs, grouped.cpu()) < 1e-2
+
+
+def test_wider_model_long_prompt_reaches_the_large_tile_paths():
+    """Width 512, 64-wide heads, a 2048-wide dense feed-forward and 256-wide experts over 1100 tokens in bf16: the prompt runs the
+    paired-CTA products with bias and gated epilogues, the tensor-core attention with every window edge inside the prompt and
+    the per-expert dense runs; then 20 decoded tokens."""
+    cfg = make_cfg([layer("attention_2", dense(2048, 2.5), heads=8, kv_heads=2, dim=64, vdim=64, size=300),
+                    layer("attention", moe(experts=4, top=2, ff=256, shared=512), heads=8, kv_heads=4, dim=64, vdim=64, size=200),
+                    layer("attention_3", moe(experts=4, top=2, ff=256, shared=0), heads=4, kv_heads=1, dim=128, vdim=128, size=500, keep_first=7)],
+                   width=512, vocab=1000)
+    w = O.random_weights(cfg, seed=77)
+    tk = toks(1120, 1000, 3)
+    ref = O.forward(cfg, w, tk)
+    eng = engine_for(cfg, w, torch.bfloat16, max_tokens=1280, slots=2)
+    poison(eng)
+    got = run_cut(eng, "a", tk, [1100, 1])
+    assert close(got, ref, torch.bfloat16)
