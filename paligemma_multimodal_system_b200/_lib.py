@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PG_LIB_PATH") or os.path.join(_HERE, "libpaligemma_b200.so")  # PG_LIB_PATH: A/B builds (profiling)
 
 EPI_BF16, EPI_F32, EPI_ATOMIC_F32, EPI_GEGLU = 0, 1, 2, 3
+ABI_VERSION = 3  # pg_abi_version() of the library these signatures describe
 
 _ERRORS = {-1: "PG_ERR_ARG", -2: "PG_ERR_CUDA", -3: "PG_ERR_DRIVER", -4: "PG_ERR_TMAP", -5: "PG_ERR_ARCH"}
 
@@ -129,6 +130,9 @@ def lib():
             fn = getattr(l, name)
             fn.argtypes = args
             fn.restype = _RESTYPE.get(name, i32)
+        if l.pg_abi_version() != ABI_VERSION:
+            raise RuntimeError(f"{LIB_PATH} has ABI version {l.pg_abi_version()}, this package expects {ABI_VERSION}: rebuild it with "
+                               "`python -m paligemma_multimodal_system_b200.build --force`")
         _lib = l
         if os.environ.get("PG_PDL", "1") == "0":
             l.pg_set_pdl(0)
