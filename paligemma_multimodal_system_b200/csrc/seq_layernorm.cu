@@ -230,6 +230,117 @@ __global__ void __launch_bounds__(256) layernorm_shift_vec_kernel(const float* _
   }
 }
 
+// Many rows (prompt portions): a CTA walks R CONSECUTIVE rows.  The next row's loads are in flight while the current one is
+// reduced and written, and a of the row just finished stays in registers as the next row's "previous token", so a row is read
+// once; only a chunk's first row, when it continues an entry, rebuilds a of the row before it.  Slot ownership as above.
+__device__ __forceinline__ float block_sum1(float a, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = a;
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) s += red[w];
+  return s;
+}
+
+template <int VT>
+__device__ __forceinline__ void row_stats(const float4 (&v)[VT], int D, float eps, float* red, float& mean, float& rstd) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < VT; ++i) s += sum4(v[i]);  // lanes past D hold zeros
+  mean = block_sum1(s, red) / (float)D;
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < VT; ++i)
+    if (4 * (threadIdx.x + 256 * i) < D) q += dev4(v[i], mean);
+  rstd = 1.0f / sqrtf(block_sum1(q, red) / (float)D + eps);
+}
+
+template <int VT>
+__device__ __forceinline__ void load_row(const float* __restrict__ src, int D, float4 (&v)[VT]) {
+#pragma unroll
+  for (int i = 0; i < VT; ++i) {
+    const int d = 4 * (threadIdx.x + 256 * i);
+    v[i] = d < D ? ld4(src + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <typename TO, int VT>
+__global__ void __launch_bounds__(256) layernorm_shift_rows_kernel(const float* __restrict__ x, const float* __restrict__ w1, const float* __restrict__ b1,
+                                                                   const float* __restrict__ shift, const float* __restrict__ w2,
+                                                                   const float* __restrict__ b2, TO* __restrict__ out1, TO* __restrict__ out2,
+                                                                   float* __restrict__ state, const int* __restrict__ pos,
+                                                                   const int* __restrict__ row_entry, const int* __restrict__ entry_row0,
+                                                                   const int* __restrict__ entry_n, const int* __restrict__ entry_slot, int rows, int R, int D,
+                                                                   float eps) {
+  __shared__ float red[8];
+  const int t0 = blockIdx.x * R, t1 = min(rows, t0 + R);
+  if (t0 >= rows) return;
+  float4 v[VT], vn[VT], ap[VT];
+  load_row<VT>(x + (long long)t0 * D, D, vn);
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int i = 0; i < VT; ++i) v[i] = vn[i];
+    if (t + 1 < t1) load_row<VT>(x + (long long)(t + 1) * D, D, vn);  // in flight during this row's reductions
+    float mean, rstd;
+    row_stats<VT>(v, D, eps, red, mean, rstd);
+    const int e = row_entry[t];
+    const int first = entry_row0[e], n = entry_n[e];
+    const bool owner = t == first;
+    float* slot = state + (long long)entry_slot[e] * D;
+    if (pos[t] == 0) {
+#pragma unroll
+      for (int i = 0; i < VT; ++i) ap[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else if (owner) {
+      load_row<VT>(slot, D, ap);
+    } else if (t == t0) {  // the chunk starts inside an entry: a of the row before, rebuilt from x
+      float pm, pr;
+      load_row<VT>(x + (long long)(t - 1) * D, D, ap);
+      row_stats<VT>(ap, D, eps, red, pm, pr);
+#pragma unroll
+      for (int i = 0; i < VT; ++i) {
+        const int d = 4 * (threadIdx.x + 256 * i);
+        if (d < D) ap[i] = ln4(ap[i], pm, pr, ld4(w1 + d), ld4(b1 + d));
+      }
+    }  // else: ap holds a of row t - 1 of the same entry, left by the previous iteration
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+      const int d = 4 * (threadIdx.x + 256 * i);
+      if (d >= D) continue;
+      const float4 a = ln4(v[i], mean, rstd, ld4(w1 + d), ld4(b1 + d));
+      const float4 sh = ld4(shift + d);
+      st4(out1 + (long long)t * D + d, make_float4(fmaf(ap[i].x - a.x, sh.x, a.x), fmaf(ap[i].y - a.y, sh.y, a.y), fmaf(ap[i].z - a.z, sh.z, a.z),
+                                                   fmaf(ap[i].w - a.w, sh.w, a.w)));
+      if (out2 != nullptr) st4(out2 + (long long)t * D + d, ln4(v[i], mean, rstd, ld4(w2 + d), ld4(b2 + d)));
+      if (owner && n == 1) st4(slot + d, a);  // the same thread read slot[d .. d + 3] above
+      ap[i] = a;
+    }
+    if (owner && n > 1) {  // this CTA alone touches the slot: a of the entry's last row
+      float4 u[VT];
+      float lm, lr;
+      load_row<VT>(x + (long long)(first + n - 1) * D, D, u);
+      row_stats<VT>(u, D, eps, red, lm, lr);
+#pragma unroll
+      for (int i = 0; i < VT; ++i) {
+        const int d = 4 * (threadIdx.x + 256 * i);
+        if (d < D) st4(slot + d, ln4(u[i], lm, lr, ld4(w1 + d), ld4(b1 + d)));
+      }
+    }
+  }
+}
+
+template <typename TO, int VT>
+int launch_ln_rows(const float* x, const float* w1, const float* b1, const float* shift, const float* w2, const float* b2, void* out1, void* out2, float* state,
+                   const int* pos, const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_slot, int rows, int R, int D, float eps,
+                   cudaStream_t st) {
+  layernorm_shift_rows_kernel<TO, VT><<<(rows + R - 1) / R, 256, 0, st>>>(x, w1, b1, shift, w2, b2, static_cast<TO*>(out1), static_cast<TO*>(out2), state, pos,
+                                                                          row_entry, entry_row0, entry_n, entry_slot, rows, R, D, eps);
+  pg_count_launch(1);
+  return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
+}
+
 template <typename TO, int VT>
 int launch_ln_vec(const float* x, const float* w1, const float* b1, const float* shift, const float* w2, const float* b2, void* out1, void* out2, float* state,
                   const int* pos, const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_slot, int rows, int D, float eps,
@@ -276,6 +387,18 @@ extern "C" int pg_layernorm_shift(const float* x, const float* w1, const float* 
 #define PG_LNV(VT)                                                                                                                                      \
   return out_f32 ? launch_ln_vec<float, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, D, eps, st) \
                  : launch_ln_vec<bf16, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, D, eps, st)
+    // prompt portions: chunks of consecutive rows, about two waves of four CTAs per SM
+    const int R = min(32, (rows + 8 * pg::num_sms() - 1) / (8 * pg::num_sms()));
+    if (shift != nullptr && R >= 2) {
+#define PG_LNR(VT)                                                                                                                                          \
+  return out_f32 ? launch_ln_rows<float, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, R, D, eps, st) \
+                 : launch_ln_rows<bf16, VT>(x, w1, b1, shift, w2, b2, out1, out2, state, pos, row_entry, entry_row0, entry_n, entry_slot, rows, R, D, eps, st)
+      if (D <= 1024) PG_LNR(1);
+      if (D <= 2048) PG_LNR(2);
+      if (D <= 4096) PG_LNR(4);
+      PG_LNR(8);
+#undef PG_LNR
+    }
     if (D <= 1024) PG_LNV(1);
     if (D <= 2048) PG_LNV(2);
     if (D <= 4096) PG_LNV(4);
