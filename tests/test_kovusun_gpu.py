@@ -120,21 +120,26 @@ def _entries(layout, lens_ctx, dtype, skip_pages=2):
 # ----------------------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ----------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("D", [40, 72, 257, 1024])
+@pytest.mark.parametrize("D,lens,plans", [(40, [23, 9, 14], [[5, 1, 2, 15], [1] * 9, [14]]), (72, [23, 9, 14], [[5, 1, 2, 15], [1] * 9, [14]]),
+                                          (257, [23, 9, 14], [[5, 1, 2, 15], [1] * 9, [14]]), (1024, [23, 9, 14], [[5, 1, 2, 15], [1] * 9, [14]]),
+                                          # steps of thousands of rows: the kernel walks chunks of consecutive rows per CTA, chunk borders fall
+                                          # inside entries, on their first rows and on their last ones
+                                          (72, [5000, 9, 2703], [[4000, 1, 2, 997], [1] * 9, [700, 2001, 2]]),
+                                          (1280, [2500, 3, 1301], [[1, 2400, 99], [1, 1, 1], [1300, 1]])])
 @pytest.mark.parametrize("f32", [True, False])
-def test_two_norms_and_token_shift_in_portions(D, f32):
+def test_two_norms_and_token_shift_in_portions(D, lens, plans, f32):
     """Three sequences advance together in unequal portions (one of them token by token); the mixer's input must equal the
     whole-sequence oracle at every position, whatever the state slots held before."""
     from paligemma_multimodal_system_b200 import seq_ops
     from paligemma_multimodal_system_b200.cache import SequenceStore
     g = torch.Generator().manual_seed(D)
-    eps, lens = 1e-5, [23, 9, 14]
+    eps = 1e-5
     xs = [3.0 + 2.0 * torch.randn(n, D, generator=g) for n in lens]
     w1, b1, w2, b2 = (torch.randn(D, generator=g) for _ in range(4))
     sh = torch.rand(D, generator=g)
     ref1 = [O.token_shift(O.layer_norm(x, w1, b1, eps), sh) for x in xs]
     ref2 = [O.layer_norm(x, w2, b2, eps) for x in xs]
-    store = SequenceStore([("state", (D,))], max_tokens=256, num_slots=4, dtype=torch.float32)
+    store = SequenceStore([("state", (D,))], max_tokens=sum(lens) + 256, num_slots=4, dtype=torch.float32)
     store.state[0].fill_(1e4)
     store.admit("unused")
     for i in range(3):
@@ -142,7 +147,6 @@ def test_two_norms_and_token_shift_in_portions(D, f32):
     dt = torch.float32 if f32 else torch.bfloat16
     got1, got2 = [[] for _ in lens], [[] for _ in lens]
     fed = [0, 0, 0]
-    plans = [[5, 1, 2, 15], [1] * 9, [14]]
     step = 0
     while any(fed[i] < lens[i] for i in range(3)):
         es, rows = [], []
@@ -472,12 +476,12 @@ def test_long_context_decode_with_key_splits_and_kept_first_keys():
                     layer("attention", moe(experts=4, top=2, ff=16, shared=16), heads=2, kv_heads=2, dim=16, vdim=16, size=1100),
                     layer("attention_2", None, heads=2, kv_heads=2, dim=16, vdim=16, size=64)], width=32, vocab=50)
     w = O.random_weights(cfg, seed=5)
-    tk = toks(1200, 50, 9)
-    ref = O.forward(cfg, w, tk)[-40:]
-    eng = engine_for(cfg, w, torch.float32, max_tokens=1280, slots=1)
+    tk = toks(1300, 50, 9)
+    full = O.forward(cfg, w, tk)
+    eng = engine_for(cfg, w, torch.float32, max_tokens=1344, slots=1)
     poison(eng)
-    got = run_cut(eng, "a", tk, [1160, 1])[-40:]
-    assert rel_err(got, ref) < F32_TOL
+    got = run_cut(eng, "a", tk, [1260, 1])  # a portion long enough for the row-chunked norm kernel, then 40 decoded tokens
+    assert rel_err(got[-40:], full[-40:]) < F32_TOL and rel_err(got, full) < F32_TOL
 
 
 def test_first_tokens_of_a_sequence(base):
