@@ -619,3 +619,14 @@ def test_wider_model_long_prompt_reaches_the_large_tile_paths():
     poison(eng)
     got = run_cut(eng, "a", tk, [1100, 1])
     assert close(got, ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("window,keep,ctx,n", [(4500, 0, 5000, 1), (3000, 6, 5000, 1), (4097, 2, 4990, 11)])
+def test_needle_at_window_edges_in_a_long_context_with_many_key_splits(window, keep, ctx, n):
+    last = ctx + n - 1
+    for needle, seen in ((last - window + 1, True), (last - window, False), (keep - 1, True), (keep, False)):
+        if needle < 0:
+            continue
+        got, ref = _needle_case(window, keep, ctx, n, needle, dim=64, vdim=64)
+        assert rel_err(got, ref) < 1e-4, (needle, seen)
+        assert bool(got[-1].abs().max() > 25.0) == seen, (needle, seen)
