@@ -300,10 +300,25 @@ int pg_layernorm_shift(const float* x, const float* w1, const float* b1, const f
 int pg_glu(const void* gu, long long ldgu, void* out, long long ldo, int rows, int F, int kind, float limit, float alpha, int act_f32,
            void* stream);
 
-/* The same product with out[t, f] = sum + bias[f] (bias fp32 [features] or NULL) + (accumulate != 0 ? out[t, f] : 0): projections
- * with biases and projections that add into the fp32 residual stream. */
+/* The same product with out[t, f] = (sum + bias[f]) * scale (bias fp32 [features] or NULL) + (accumulate != 0 ? out[t, f] : 0):
+ * projections with biases and projections that add into the fp32 residual stream (scale: a residual multiplier). */
 int pg_gemm_simt_bias(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, const float* bias,
-                      int accumulate, int tokens, int features, int K, int in_f32, int out_f32, void* stream);
+                      int accumulate, float scale, int tokens, int features, int K, int in_f32, int out_f32, void* stream);
+
+/* ---- normalised residual read through a short causal convolution; polynomial-of-norms activation ------------------------------
+ * pg_rmsnorm_conv: h[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w (w: fp32 [D], or ONE number when w_scalar != 0); out_h[t] = h[t];
+ *   out_conv[t, c] = h[t, c] + sum_{j < taps} conv_w[c * taps + j] * h[t - taps + 1 + j, c], where rows before the sequence's
+ *   start are zeros and rows before this step come from state (fp32 [slots, taps - 1, D]: the last taps - 1 rows h of the
+ *   sequence in slot entry_slot[e], oldest first; ignored when entry_ctx[e] == 0; rewritten here).  conv_w NULL: no convolution,
+ *   no state (a bare norm; out_conv, when given, equals out_h).  Either output may be NULL.  taps <= 8.
+ * pg_polynorm: out[t, f] = a N(z)[f] + b N(z^2)[f] + c N(z^3)[f] + e with (a, b, c, e) = coef[0..3] (fp32, device), powers taken
+ *   element by element and N(v) = v / sqrt(mean_f(v^2) + eps); z and out in the activation type, statistics fp32.
+ * pg_sigmoid_gate_mul: y[t, c] *= sigmoid(gate[t, c]) for c < n (both in the activation type, pitches ldy / ldg). */
+int pg_rmsnorm_conv(const float* x, const float* w, int w_scalar, const float* conv_w, int taps, float* state, void* out_h, void* out_conv,
+                    const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* entry_slot, int rows, int D,
+                    float eps, int out_f32, void* stream);
+int pg_polynorm(const void* z, long long ldz, const float* coef, void* out, long long ldo, int rows, int F, float eps, int act_f32, void* stream);
+int pg_sigmoid_gate_mul(void* y, long long ldy, const void* gate, long long ldg, int rows, int n, int act_f32, void* stream);
 
 /* grid.z = batch independent products out_b = x_b w_b^T; operand b starts batch_* elements after operand b - 1 (per-head
  * projections: x a column slice per head, w one matrix per head). */
@@ -343,11 +358,12 @@ int pg_side_gate(const float* z, long long ldz, const int* tokens, const void* t
  * root mean square over vdim.  q goes to q_out [rows, H * dim]; k and v go to cache row
  * page_table[row_entry[t] * max_pages + pos[t] / page] * page + pos[t] % page of k_pages [.., G * dim] / v_pages [.., G * vdim].
  * norm_qk == 0 / norm_v == 0 leave out the q/k norm / the value norm; q_norm, k_norm NULL: a norm without a weight; k_pages and
- * v_pages both NULL: the row holds queries only (a layer that attends over another layer's cache). */
+ * v_pages both NULL: the row holds queries only (a layer that attends over another layer's cache).  v_from_k != 0: the row is
+ * [q heads | k heads | ...] and value head g is key head g as projected, before norm and rotation (vdim == dim). */
 int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                     int page, const double* freq, const float* q_norm, const float* k_norm, void* q_out, void* k_pages,
-                    void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int norm_qk, int norm_v, int act_f32,
-                    void* stream);
+                    void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int norm_qk, int norm_v, int v_from_k,
+                    int act_f32, void* stream);
 
 /* Optional parts of a softmax attention's score and mask, read by pg_attn_ragged, pg_attn_ragged_mma, pg_attn_decode and
  * pg_attn_decode_merge (a NULL pointer or an all-zero struct: plain causal attention).  With i the query's position and j a key's:
@@ -433,6 +449,8 @@ int pg_stream_mix_norm(float* xs, const float* y, long long ldy, const float* mi
  * pg_latent_prepare: proj[t] = [q latent (q_rank) | kv latent (rank) | key part (rot) | ...] (pitch ld).  cq_out[t, :] =
  *   rms(q latent) * q_norm (skipped when q_rank == 0); cache row of position pos[t] <- [rms(kv latent) * c_norm | key part with
  *   its first rot_dims dimensions rotated in interleaved pairs by pos[t] * freq[i]].  pages: [.., page, rank + rot].
+ *   rot_gain multiplies the cosines and sines (1: a pure rotation).  pages NULL (q_rank > 0): only cq_out is made -- a layer that
+ *   reads another layer's cached rows; proj then holds [q latent | ...].
  * pg_rotate_heads: for every row and head, n elements at src[t * ld_src + h * head_stride_src ..] are copied to
  *   dst[t * ld_dst + h * head_stride_dst ..] with the first rot_dims rotated the same way.
  * pg_latent_gather: lat[dense_row0[e] + j, 0:rank] <- cached row j of entry e, j < ctx + n (width = elements per cache row).
@@ -441,9 +459,9 @@ int pg_stream_mix_norm(float* xs, const float* y, long long ldy, const float* mi
  *   k_out[row, h, :] = [plain (dim) | cached rotated part (rot)], v_out[row, h, :]. */
 int pg_latent_prepare(const void* proj, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                       int page, const double* freq, const float* q_norm, const float* c_norm, void* cq_out, void* pages, int rows,
-                      int q_rank, int rank, int rot, int rot_dims, float eps, int act_f32, void* stream);
+                      int q_rank, int rank, int rot, int rot_dims, float eps, float rot_gain, int act_f32, void* stream);
 int pg_rotate_heads(const void* src, long long ld_src, long long head_stride_src, void* dst, long long ld_dst, long long head_stride_dst,
-                    const int* pos, const double* freq, int rows, int H, int n, int rot_dims, int act_f32, void* stream);
+                    const int* pos, const double* freq, int rows, int H, int n, int rot_dims, float rot_gain, int act_f32, void* stream);
 int pg_latent_gather(const void* pages, const int* page_table, int max_pages, int page, const int* dense_row0, const int* entry_n,
                      const int* entry_ctx, void* lat, int entries, int max_len, int rank, int width, int act_f32, void* stream);
 int pg_latent_pack_kv(const void* up, long long ld_up, const void* pages, const int* page_table, int max_pages, int page,

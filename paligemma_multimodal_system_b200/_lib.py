@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PG_LIB_PATH") or os.path.join(_HERE, "libpaligemma_b200.so")  # PG_LIB_PATH: A/B builds (profiling)
 
 EPI_BF16, EPI_F32, EPI_ATOMIC_F32, EPI_GEGLU = 0, 1, 2, 3
-ABI_VERSION = 3  # pg_abi_version() of the library these signatures describe
+ABI_VERSION = 4  # pg_abi_version() of the library these signatures describe
 
 _ERRORS = {-1: "PG_ERR_ARG", -2: "PG_ERR_CUDA", -3: "PG_ERR_DRIVER", -4: "PG_ERR_TMAP", -5: "PG_ERR_ARCH"}
 
@@ -70,7 +70,7 @@ SIGNATURES = {
     "pg_rmsnorm_gate": [p, p, p, i64, p, i32, i32, f32, i32, p],
     "pg_geglu": [p, i64, p, i64, i32, i32, i32, p],
     "pg_side_gate": [p, i64, p, p, i64, i32, p, i64, i32, i32, i32, i32, p],
-    "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, p],
+    "pg_attn_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, f32, i32, i32, i32, i32, p],
     "pg_attn_ragged": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, i64, i64, i32, p, p],
     "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p, p],
     "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i64, i64, i32, p, p],
@@ -81,8 +81,8 @@ SIGNATURES = {
     "pg_gemm_simt_batched": [p, i64, i64, p, i64, i64, p, i64, i64, i32, i32, i32, i32, i32, i32, p],
     "pg_embed_streams": [p, p, i64, p, i32, i32, i32, f32, i32, p],
     "pg_stream_mix_norm": [p, p, i64, p, p, p, p, p, i32, i32, i32, f32, i32, p],
-    "pg_latent_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, f32, i32, p],
-    "pg_rotate_heads": [p, i64, i64, p, i64, i64, p, p, i32, i32, i32, i32, i32, p],
+    "pg_latent_prepare": [p, i64, p, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, f32, f32, i32, p],
+    "pg_rotate_heads": [p, i64, i64, p, i64, i64, p, p, i32, i32, i32, i32, f32, i32, p],
     "pg_latent_gather": [p, p, i32, i32, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_latent_pack_kv": [p, i64, p, p, i32, i32, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, p],
     "pg_relu2": [p, i64, i32, i32, i32, p],
@@ -93,7 +93,10 @@ SIGNATURES = {
     "pg_moe_gather_rows": [p, i64, p, p, i32, p, i64, i32, i32, i32, p],
     "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
     "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p, i64, i32, p],
-    "pg_gemm_simt_bias": [p, i64, p, i64, p, i64, p, i32, i32, i32, i32, i32, i32, p],
+    "pg_gemm_simt_bias": [p, i64, p, i64, p, i64, p, i32, f32, i32, i32, i32, i32, i32, p],
+    "pg_rmsnorm_conv": [p, p, i32, p, i32, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],
+    "pg_polynorm": [p, i64, p, p, i64, i32, i32, f32, i32, p],
+    "pg_sigmoid_gate_mul": [p, i64, p, i64, i32, i32, i32, p],
     "pg_layernorm_shift": [p, p, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],
     "pg_glu": [p, i64, p, i64, i32, i32, i32, f32, f32, i32, p],
 }
@@ -239,8 +242,8 @@ def rmsnorm(x, w, out_bf16, eps=1e-6):
     check(lib().pg_rmsnorm(x.data_ptr(), w.data_ptr(), out_bf16.data_ptr(), rows, D, float(eps), stream()), "pg_rmsnorm")
 
 
-def gemm_residual(x, w, h, bias=None):
-    """h += x @ w.T (+ bias): the residual-stream GEMMs (out_proj / fc2 / o_proj / down_proj).  With enough output tiles
+def gemm_residual(x, w, h, bias=None, scale=1.0):
+    """h += (x @ w.T + bias) * scale: the residual-stream GEMMs (out_proj / fc2 / o_proj / down_proj).  With enough output tiles
     the epilogue adds the fp32 residual in place; with few tiles (small token counts: latency path, decode) the K
     dimension is split over CTAs and the partials are red.add-ed into h so that the whole GPU streams the weights."""
     T, K = x.shape
@@ -259,6 +262,6 @@ def gemm_residual(x, w, h, bias=None):
             # activation tile from L2 too often.
             tiles = ((T + 127) // 128) * ((F + 63) // 64)
     if tiles >= 96 or kb < 8 or T > 512:  # (large-batch prefill keeps the deterministic, atomics-free epilogue)
-        return gemm(x, w, h, mode=EPI_F32, bias=bias, resid=h, swap=swap)
+        return gemm(x, w, h, mode=EPI_F32, bias=bias, resid=h, swap=swap, scale=scale)
     split = max(1, min(kb // 4, (2 * 148 if swap else 148) // tiles))
-    return gemm(x, w, h, mode=EPI_ATOMIC_F32, bias=bias, swap=swap, split_k=split)
+    return gemm(x, w, h, mode=EPI_ATOMIC_F32, bias=bias, swap=swap, split_k=split, scale=scale)

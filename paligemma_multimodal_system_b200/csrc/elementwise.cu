@@ -434,7 +434,7 @@ int pg_pdl_enabled(void) { return g_pdl; }
 extern "C" int pg_set_pdl(int on) { g_pdl = on ? 1 : 0; return PG_OK; }
 extern "C" long long pg_launch_count(void) { return g_launches; }
 
-extern "C" int pg_abi_version(void) { return 3; }
+extern "C" int pg_abi_version(void) { return 4; }
 extern "C" int pg_num_sms(void) { return pg::num_sms(); }
 
 extern "C" int pg_check_device(void) {

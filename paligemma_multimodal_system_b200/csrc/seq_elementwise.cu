@@ -57,7 +57,7 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x, long long ldx, const TI* __restrict__ w, long long ldw,
                                                         TO* __restrict__ out, long long ldo, int T, int F, int K, long long bsx = 0,
                                                         long long bsw = 0, long long bso = 0, const float* __restrict__ bias = nullptr,
-                                                        int accumulate = 0) {
+                                                        int accumulate = 0, float scale = 1.0f) {
   __shared__ float xs[16][64 + 4];
   __shared__ float ws[16][64 + 4];
   x += blockIdx.z * bsx;  // batched form: grid.z independent products with their own operand offsets
@@ -93,6 +93,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TI* __restrict__ x
       if (t < T && f < F) {
         float v = acc[i][j];
         if (bias != nullptr) v += bias[f];
+        v *= scale;
         if (accumulate) v += ld_f(out, (long long)t * ldo + f);
         st_f(out, (long long)t * ldo + f, v);
       }
@@ -274,17 +275,17 @@ extern "C" int pg_gemm_simt(const void* x, long long ldx, const void* w, long lo
 }
 
 extern "C" int pg_gemm_simt_bias(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ldo, const float* bias,
-                                 int accumulate, int tokens, int features, int K, int in_f32, int out_f32, void* stream) {
+                                 int accumulate, float scale, int tokens, int features, int K, int in_f32, int out_f32, void* stream) {
   if (tokens <= 0 || features <= 0 || K <= 0 || x == nullptr || w == nullptr || out == nullptr) return PG_ERR_ARG;
   dim3 grid((features + 63) / 64, (tokens + 63) / 64);
   if (grid.y > 65535) return PG_ERR_ARG;
   cudaStream_t st = PG_ST(stream);
   if (in_f32 && out_f32)
-    gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
+    gemm_simt_kernel<float, float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate, scale);
   else if (!in_f32 && out_f32)
-    gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
+    gemm_simt_kernel<bf16, float><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<float*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate, scale);
   else if (!in_f32 && !out_f32)
-    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate);
+    gemm_simt_kernel<bf16, bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), ldx, static_cast<const bf16*>(w), ldw, static_cast<bf16*>(out), ldo, tokens, features, K, 0, 0, 0, bias, accumulate, scale);
   else
     return PG_ERR_ARG;
   PG_RET();

@@ -50,13 +50,11 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const TA* __restric
                                                              const int* __restrict__ row_entry, const int* __restrict__ page_table, int max_pages,
                                                              int page, const double* __restrict__ freq, const float* __restrict__ qn,
                                                              const float* __restrict__ cn, TA* __restrict__ cq_out, TA* __restrict__ pages,
-                                                             int q_rank, int rank, int rot, int rot_dims, float eps) {
+                                                             int q_rank, int rank, int rot, int rot_dims, float eps, float rot_gain) {
   __shared__ float red[4];
   const long long t = blockIdx.x;
   const TA* row = proj + t * ld;
   const int p = pos[t];
-  const long long pg_row = (long long)page_table[(long long)row_entry[t] * max_pages + p / page] * page + p % page;
-  TA* dst = pages + pg_row * (long long)(rank + rot);
   if (q_rank > 0) {
     float s = 0.f;
     for (int d = threadIdx.x; d < q_rank; d += 128) { const float v = ldv(row, d); s = fmaf(v, v, s); }
@@ -64,6 +62,9 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const TA* __restric
     const float inv = 1.0f / sqrtf(s / (float)q_rank + eps);
     for (int d = threadIdx.x; d < q_rank; d += 128) stv(cq_out, t * q_rank + d, ldv(row, d) * inv * qn[d]);
   }
+  if (pages == nullptr) return;  // a layer that attends over another layer's cached rows prepares its query latent only
+  const long long pg_row = (long long)page_table[(long long)row_entry[t] * max_pages + p / page] * page + p % page;
+  TA* dst = pages + pg_row * (long long)(rank + rot);
   {
     float s = 0.f;
     for (int d = threadIdx.x; d < rank; d += 128) { const float v = ldv(row, q_rank + d); s = fmaf(v, v, s); }
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const TA* __restric
     if (d + 1 < rot_dims) {
       double sn, c;
       sincos((double)p * freq[i], &sn, &c);
-      const float cf = (float)c, sf = (float)sn;
+      const float cf = (float)c * rot_gain, sf = (float)sn * rot_gain;
       const float ra = a * cf - b * sf, rb = b * cf + a * sf;
       a = ra; b = rb;
     }
@@ -90,15 +91,16 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const TA* __restric
 // grid (rows, head blocks); thread <-> (head, pair)
 template <typename TA>
 __global__ void rotate_heads_kernel(const TA* __restrict__ src, long long ld_src, long long hs_src, TA* __restrict__ dst, long long ld_dst,
-                                    long long hs_dst, const int* __restrict__ pos, const double* __restrict__ freq, int H, int n, int rot_dims) {
+                                    long long hs_dst, const int* __restrict__ pos, const double* __restrict__ freq, int H, int n, int rot_dims,
+                                    float rot_gain) {
   extern __shared__ float cs[];  // cos, sin of the row's rot_dims/2 angles
   const long long t = blockIdx.x;
   const int p = pos[t];
   for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
     double sn, c;
     sincos((double)p * freq[i], &sn, &c);
-    cs[i] = (float)c;
-    cs[rot_dims / 2 + i] = (float)sn;
+    cs[i] = (float)c * rot_gain;
+    cs[rot_dims / 2 + i] = (float)sn * rot_gain;
   }
   __syncthreads();
   const int pairs = (n + 1) / 2;
@@ -160,29 +162,30 @@ __global__ void latent_pack_kv_kernel(const TA* __restrict__ up, long long ld_up
 
 extern "C" int pg_latent_prepare(const void* proj, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                                  int page, const double* freq, const float* q_norm, const float* c_norm, void* cq_out, void* pages, int rows,
-                                 int q_rank, int rank, int rot, int rot_dims, float eps, int act_f32, void* stream) {
+                                 int q_rank, int rank, int rot, int rot_dims, float eps, float rot_gain, int act_f32, void* stream) {
   if (rows <= 0 || q_rank < 0 || rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || page <= 0) return PG_ERR_ARG;
+  if (pages == nullptr && q_rank == 0) return PG_ERR_ARG;
   if (act_f32)
     latent_prepare_kernel<float><<<rows, 128, 0, PG_ST(stream)>>>(static_cast<const float*>(proj), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                  q_norm, c_norm, static_cast<float*>(cq_out), static_cast<float*>(pages), q_rank, rank,
-                                                                 rot, rot_dims, eps);
+                                                                 rot, rot_dims, eps, rot_gain);
   else
     latent_prepare_kernel<bf16><<<rows, 128, 0, PG_ST(stream)>>>(static_cast<const bf16*>(proj), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                 q_norm, c_norm, static_cast<bf16*>(cq_out), static_cast<bf16*>(pages), q_rank, rank,
-                                                                rot, rot_dims, eps);
+                                                                rot, rot_dims, eps, rot_gain);
   PG_RET();
 }
 
 extern "C" int pg_rotate_heads(const void* src, long long ld_src, long long head_stride_src, void* dst, long long ld_dst, long long head_stride_dst,
-                               const int* pos, const double* freq, int rows, int H, int n, int rot_dims, int act_f32, void* stream) {
+                               const int* pos, const double* freq, int rows, int H, int n, int rot_dims, float rot_gain, int act_f32, void* stream) {
   if (rows <= 0 || H <= 0 || n <= 0 || rot_dims < 0 || rot_dims > n || (rot_dims & 1)) return PG_ERR_ARG;
   const size_t smem = (size_t)(rot_dims + 2) * sizeof(float);
   if (act_f32)
     rotate_heads_kernel<float><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const float*>(src), ld_src, head_stride_src, static_cast<float*>(dst),
-                                                                  ld_dst, head_stride_dst, pos, freq, H, n, rot_dims);
+                                                                  ld_dst, head_stride_dst, pos, freq, H, n, rot_dims, rot_gain);
   else
     rotate_heads_kernel<bf16><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const bf16*>(src), ld_src, head_stride_src, static_cast<bf16*>(dst), ld_dst,
-                                                                 head_stride_dst, pos, freq, H, n, rot_dims);
+                                                                 head_stride_dst, pos, freq, H, n, rot_dims, rot_gain);
   PG_RET();
 }
 

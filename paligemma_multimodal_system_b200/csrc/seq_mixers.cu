@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
                                                            int page, const double* __restrict__ freq, const float* __restrict__ qn,
                                                            const float* __restrict__ kn, TA* __restrict__ q_out, TA* __restrict__ k_pages,
                                                            TA* __restrict__ v_pages, int H, int G, int dim, int vdim, int rot, float eps,
-                                                           int norm_qk, int norm_v) {
+                                                           int norm_qk, int norm_v, int v_from_k) {
   extern __shared__ float cs[];  // cos[rot/2], sin[rot/2]
   const long long t = blockIdx.x;
   const int p = pos[t];
@@ -78,8 +78,10 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(const TA* __restrict_
   for (int vec = warp; vec < nvec; vec += nw) {
     const bool is_q = vec < H, is_k = !is_q && vec < H + G;
     const int n = (is_q || is_k) ? dim : vdim;
+    // v_from_k: the row has no value columns; value head g is key head g as projected (vdim == dim), before norm and rotation
     const long long off = is_q ? (long long)vec * dim : is_k ? (long long)H * dim + (long long)(vec - H) * dim
-                                                            : (long long)(H + G) * dim + (long long)(vec - H - G) * vdim;
+                          : v_from_k ? (long long)H * dim + (long long)(vec - H - G) * dim
+                                     : (long long)(H + G) * dim + (long long)(vec - H - G) * vdim;
     // lane <-> pairs (2i, 2i+1): a rotation never needs another lane's element; an odd last element is a pair with a zero
     float inv = 1.0f;
     if ((is_q || is_k) ? norm_qk : norm_v) {
@@ -775,18 +777,19 @@ __global__ void __launch_bounds__(256, 2) linear_attn_chunked_kernel(const TA* _
 extern "C" int pg_attn_prepare(const void* qkv, long long ld, const int* pos, const int* row_entry, const int* page_table, int max_pages,
                                int page, const double* freq, const float* q_norm, const float* k_norm, void* q_out, void* k_pages,
                                void* v_pages, int rows, int H, int G, int dim, int vdim, int rot_dims, float eps, int norm_qk, int norm_v,
-                               int act_f32, void* stream) {
+                               int v_from_k, int act_f32, void* stream) {
   if (rows <= 0 || H <= 0 || G <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || page <= 0) return PG_ERR_ARG;
+  if (v_from_k && vdim != dim) return PG_ERR_ARG;
   if ((k_pages == nullptr) != (v_pages == nullptr)) return PG_ERR_ARG;
   const size_t smem = (size_t)(rot_dims + 2) * sizeof(float);
   if (act_f32)
     attn_prepare_kernel<float><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const float*>(qkv), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                   q_norm, k_norm, static_cast<float*>(q_out), static_cast<float*>(k_pages),
-                                                                  static_cast<float*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v);
+                                                                  static_cast<float*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v, v_from_k);
   else
     attn_prepare_kernel<bf16><<<rows, 128, smem, PG_ST(stream)>>>(static_cast<const bf16*>(qkv), ld, pos, row_entry, page_table, max_pages, page, freq,
                                                                  q_norm, k_norm, static_cast<bf16*>(q_out), static_cast<bf16*>(k_pages),
-                                                                 static_cast<bf16*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v);
+                                                                 static_cast<bf16*>(v_pages), H, G, dim, vdim, rot_dims, eps, norm_qk, norm_v, v_from_k);
   PG_RET();
 }
 

@@ -11,7 +11,11 @@
   GegluFeedForward        W_down(gelu_tanh(W_gate h) * W_up h)
   GluFeedForward          W_down(act(W_gate h) * W_up h) with act = silu, or the clamped form min(g, c) sigmoid(a min(g, c)) (clamp(u) + 1);
                           optional biases
+  PolyNormFeedForward     W_down P(W_up h + b) + b, P(z) = a N(z) + b N(z^2) + c N(z^3) + e with N = division by the row's root mean square
   TokenSideInput          a per-layer, per-token low-dimensional embedding gated by a projection of the residual stream
+  LatentAttention         attention over ONE cached low-rank row per token (+ one rotated key part shared by the heads); optional, each a
+                          parameter: half-split rotation layout, ramped frequency rescaling with a cos / sin gain, a sliding window, a
+                          per-element (instead of per-head) sigmoid output gate, cached rows borrowed from an earlier layer
 
 Every sub-layer gets its weights from a name -> tensor dict (`take(name)` pops and checks the shape), packs them once for a
 `Precision`, says what it keeps per sequence (`cache_spec`), and maps the step's rows h [T, D] (activation type) to
@@ -40,6 +44,29 @@ def rotary_frequencies(base: float, dims: int, scaling=None):
         mid = (1.0 - s) * f / factor + s * f
         f = torch.where(wl < orig / high, f, torch.where(wl > orig / low, f / factor, mid))
     return f
+
+
+def ramped_rotary_frequencies(base: float, dims: int, factor: float, original: float, fast: float, slow: float):
+    """Frequencies f_i = base^(-2i/dims) rescaled by pair index: with idx(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(idx(fast)), 0),
+    hi = min(ceil(idx(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * ramp_i +
+    f_i (1 - ramp_i).  Returns (frequencies float64 [dims / 2], gain) with gain = 0.1 ln(factor) + 1 multiplying every cosine and sine."""
+    def idx(turns):
+        return dims * math.log(float(original) / (2.0 * math.pi * float(turns))) / (2.0 * math.log(float(base)))
+
+    lo, hi = max(math.floor(idx(fast)), 0), min(math.ceil(idx(slow)), dims - 1)
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = float(base) ** (-2.0 * i / dims)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / float(factor) * ramp + f * (1.0 - ramp), 0.1 * math.log(float(factor)) + 1.0
+
+
+def half_to_pair_order(n: int, rot_dims: int):
+    """Index list that reorders a vector whose rotation pairs element i with element i + rot_dims / 2 so that the partners sit side by
+    side (2i, 2i + 1): rotating the reordered vector in interleaved pairs gives the reordered result of the half-split rotation.  A
+    dot product of two vectors reordered alike is unchanged, so applying this to the ROWS of the projections that make the rotated
+    query and key parts lets one rotation kernel (and one cache layout) serve both conventions."""
+    half = rot_dims // 2
+    return [i // 2 + (i % 2) * half if i < rot_dims else i for i in range(n)]
 
 
 class GatedSoftmaxAttention:
@@ -87,10 +114,14 @@ class WindowedSoftmaxAttention:
     the layer has a sink; head output times sigmoid((W_g h)_h) when it has a gate; then W_o.
 
     kv_from = j: the layer has no key / value projections and attends over layer j's cached keys and values (as layer j left
-    them, after its norm and rotation) with its own queries, window and score."""
+    them, after its norm and rotation) with its own queries, window and score.
+
+    value_is_key: there is no value projection; the values are the keys as projected, before norm and rotation (vdim == dim).
+    unit_sink: the softmax denominator is enlarged by exactly one (a sink whose logit is 0, no tensor)."""
 
     def __init__(self, width, heads, kv_heads, dim, vdim, scale, eps, window=None, keep_first=0, bias=False, qk_norm=False, rot_dims=0,
-                 rot_base=10000.0, distance_penalty=False, temperature=False, sink=False, head_gate=False, kv_from=None):
+                 rot_base=10000.0, distance_penalty=False, temperature=False, sink=False, head_gate=False, kv_from=None, value_is_key=False,
+                 unit_sink=False):
         if heads % kv_heads:
             raise ValueError("query heads must be a multiple of key/value heads")
         if rot_dims % 2 or rot_dims > dim:
@@ -102,6 +133,11 @@ class WindowedSoftmaxAttention:
         self.bias, self.qk_norm, self.rot_dims = bool(bias), bool(qk_norm), int(rot_dims)
         self.distance_penalty, self.temperature, self.sink, self.head_gate = bool(distance_penalty), bool(temperature), bool(sink), bool(head_gate)
         self.kv_from = None if kv_from is None else int(kv_from)
+        self.value_is_key, self.unit_sink = bool(value_is_key), bool(unit_sink)
+        if self.value_is_key and self.vdim != self.dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if self.unit_sink and self.sink:
+            raise ValueError("a layer has a learned sink or the unit one, not both")
         self.freq = rotary_frequencies(rot_base, rot_dims) if rot_dims else torch.zeros(1, dtype=torch.float64)
 
     def cache_spec(self):
@@ -113,9 +149,13 @@ class WindowedSoftmaxAttention:
         if self.bias:
             w["qb"] = take(pre + "q.b", (H * dim,))
         if self.kv_from is None:
-            w["k"], w["v"] = take(pre + "k", (G * dim, D)), take(pre + "v", (G * vdim, D))
+            w["k"] = take(pre + "k", (G * dim, D))
+            if not self.value_is_key:
+                w["v"] = take(pre + "v", (G * vdim, D))
             if self.bias:
-                w["kb"], w["vb"] = take(pre + "k.b", (G * dim,)), take(pre + "v.b", (G * vdim,))
+                w["kb"] = take(pre + "k.b", (G * dim,))
+                if not self.value_is_key:
+                    w["vb"] = take(pre + "v.b", (G * vdim,))
         if self.distance_penalty:
             w["r1"], w["r2"] = take(pre + "r1", (H,)), take(pre + "r2", (H,))
         if self.temperature:
@@ -130,7 +170,8 @@ class WindowedSoftmaxAttention:
     def pack(self, prec):
         w, H = self.w, self.H
         f32 = dict(device="cuda", dtype=torch.float32)
-        parts = [w["q"]] + ([w["k"], w["v"]] if self.kv_from is None else []) + ([w["g"]] if self.head_gate else [])
+        kv = [] if self.kv_from is not None else [w["k"]] if self.value_is_key else [w["k"], w["v"]]
+        parts = [w["q"]] + kv + ([w["g"]] if self.head_gate else [])
         rows = sum(t.shape[0] for t in parts)
         pad = (-rows) % 8  # zero rows up to a multiple of 8: a shape the tensor-core product takes
         self.w_in = torch.zeros(rows + pad, self.D, device="cuda", dtype=prec.dtype)
@@ -139,7 +180,7 @@ class WindowedSoftmaxAttention:
         self.b_in = None
         if self.bias:
             self.b_in = torch.zeros(rows + pad, **f32)
-            bs = torch.cat([w["qb"]] + ([w["kb"], w["vb"]] if self.kv_from is None else [])).to(**f32)
+            bs = torch.cat([w["qb"]] + ([] if self.kv_from is not None else [w["kb"]] if self.value_is_key else [w["kb"], w["vb"]])).to(**f32)
             self.b_in[:bs.numel()] = bs
         self.w_o = w["o"].to("cuda", prec.dtype).contiguous()
         self.freq_d = self.freq.to("cuda")
@@ -147,9 +188,10 @@ class WindowedSoftmaxAttention:
         def vec(name):
             return w[name].to(**f32).contiguous() if name in w else None
 
-        self.score = seq_ops.ScoreOptions(H, self.window, self.keep_first, sink=vec("sink"), dist_a=vec("r1"), dist_b=vec("r2"), head_scale=vec("temp"))
+        sink = torch.zeros(H, **f32) if self.unit_sink else vec("sink")  # exp(0) = 1 joins the denominator
+        self.score = seq_ops.ScoreOptions(H, self.window, self.keep_first, sink=sink, dist_a=vec("r1"), dist_b=vec("r2"), head_scale=vec("temp"))
 
-    def __call__(self, h, b, store, li, prec, resid=None):
+    def __call__(self, h, b, store, li, prec, resid=None, resid_scale=1.0):
         H, G, dim, vdim = self.H, self.G, self.dim, self.vdim
         proj = seq_ops.linear(h, self.w_in, prec.empty(b.T, self.w_in.shape[0]), bias=self.b_in)
         q = prec.empty(b.T, H * dim)
@@ -157,12 +199,12 @@ class WindowedSoftmaxAttention:
         src = li if own else self.kv_from
         kp, vp = store.k_pages[src], store.v_pages[src]
         seq_ops.attn_prepare(proj, b, self.freq_d, None, None, q, kp if own else None, vp if own else None, H, G, dim, vdim, self.rot_dims, self.eps,
-                             PAGE, norm_qk=self.qk_norm, norm_v=False)
+                             PAGE, norm_qk=self.qk_norm, norm_v=False, v_from_k=self.value_is_key)
         att = prec.empty(b.T, H * vdim)
         gate = proj[:, self.gate_col:] if self.head_gate else None
         seq_ops.attn_ragged(q, kp, vp, gate, att, b, H, G, dim, vdim, self.scale, 0.0, PAGE, gate_per_head=True, score=self.score)
         if resid is not None:
-            return seq_ops.linear_add(att, self.w_o, resid)
+            return seq_ops.linear_add(att, self.w_o, resid, scale=resid_scale)
         return seq_ops.linear(att, self.w_o, torch.empty(b.T, self.D, device="cuda", dtype=torch.float32))
 
 
@@ -331,46 +373,88 @@ class LatentAttention:
     c(j) -- so the paged cache is read as ONE key/value head of width rank + rot (values = its first `rank` columns) shared by
     all query heads, and nothing per head is ever stored.  Prompt portions in bf16 whose head sizes the tensor-core kernel is
     built for use the explicit-head form instead: keys / values of the entry's tokens are rebuilt from the cached rows into
-    scratch pages (the products are 3 .. 5 times smaller there)."""
+    scratch pages (the products are 3 .. 5 times smaller there).
 
-    def __init__(self, width, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, rot_dims, rot_base, eps):
+    Optional parts: rot_layout "half" -- the rotation pairs element i with i + rot_dims / 2 (the rows of the projections that make the
+    rotated parts are reordered once, see half_to_pair_order); rot_scaling = dict(factor, original, fast, slow) -- ramped frequency
+    rescaling with its cos / sin gain (ramped_rotary_frequencies); window -- key j is visible to query i when 0 <= i - j < window;
+    gate "element" -- W_g has one row per output element (H * vdim) instead of one per head; kv_from = j -- no W_dkv: the layer
+    reads the rows layer j cached (same rank, rotated part and rotation) with its own up projections, queries, window and gate."""
+
+    def __init__(self, width, heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, rot_dims, rot_base, eps, rot_layout="interleaved", rot_scaling=None,
+                 window=None, gate="head", kv_from=None):
         if rot_dims % 2 or rot_dims > rot_dim:
             raise ValueError("rotary dimensions must be even and at most the rotated key part")
+        if rot_layout not in ("interleaved", "half") or gate not in ("head", "element"):
+            raise ValueError("rot_layout is 'interleaved' or 'half', gate is 'head' or 'element'")
+        if window is not None and int(window) <= 0:
+            raise ValueError("a window holds at least the token itself")
         self.D, self.H, self.dim, self.rot, self.vdim, self.Q, self.R = width, heads, dim, rot_dim, vdim, q_rank, kv_rank
         self.scale, self.rot_dims, self.eps = float(scale), int(rot_dims), float(eps)
-        self.freq = rotary_frequencies(rot_base, rot_dims) if rot_dims else torch.zeros(1, dtype=torch.float64)
+        self.rot_layout, self.gate_kind, self.window = rot_layout, gate, (int(window) if window is not None else None)
+        self.kv_from = None if kv_from is None else int(kv_from)
+        self.rot_gain = 1.0
+        if not rot_dims:
+            self.freq = torch.zeros(1, dtype=torch.float64)
+        elif rot_scaling:
+            self.freq, self.rot_gain = ramped_rotary_frequencies(rot_base, rot_dims, *(rot_scaling[k] for k in ("factor", "original", "fast", "slow")))
+        else:
+            self.freq = rotary_frequencies(rot_base, rot_dims)
         self.explicit_prefill = True
 
     def cache_spec(self):
-        return ("latent", self.R + self.rot)
+        return None if self.kv_from is not None else ("latent", self.R + self.rot)
+
+    def cache_signature(self):
+        """What a layer that borrows this layer's rows must share with it."""
+        return (self.R, self.rot, self.rot_dims, self.rot_layout, self.rot_gain, tuple(self.freq.tolist()))
 
     def load(self, take, pre):
         H, dim, rot, vdim, Q, R, D = self.H, self.dim, self.rot, self.vdim, self.Q, self.R, self.D
-        self.w = dict(dq=take(pre + "dq", (Q, D)), qn=take(pre + "dq.norm", (Q,)), uq=take(pre + "uq", (H * (dim + rot), Q)),
-                      dkv=take(pre + "dkv", (R + rot, D)), cn=take(pre + "dkv.norm", (R,)), uk=take(pre + "uk", (H * dim, R)),
-                      uv=take(pre + "uv", (H * vdim, R)), g=take(pre + "g", (H, D)), o=take(pre + "o", (D, H * vdim)))
+        self.w = dict(dq=take(pre + "dq", (Q, D)), qn=take(pre + "dq.norm", (Q,)), uq=take(pre + "uq", (H * (dim + rot), Q)))
+        if self.kv_from is None:
+            self.w.update(dkv=take(pre + "dkv", (R + rot, D)), cn=take(pre + "dkv.norm", (R,)))
+        self.w.update(uk=take(pre + "uk", (H * dim, R)), uv=take(pre + "uv", (H * vdim, R)),
+                      g=take(pre + "g", (H * vdim if self.gate_kind == "element" else H, D)), o=take(pre + "o", (D, H * vdim)))
 
     def pack(self, prec):
-        w, H, dim, vdim, R = self.w, self.H, self.dim, self.vdim, self.R
+        w, H, dim, rot, vdim, R = self.w, self.H, self.dim, self.rot, self.vdim, self.R
         dev = dict(device="cuda", dtype=prec.dtype)
-        self.w_in = torch.cat([w["dq"], w["dkv"], w["g"]], 0).to(**dev).contiguous()
-        self.w_uq = w["uq"].to(**dev).contiguous()
+        uq, dkv = w["uq"], w.get("dkv")
+        if self.rot_layout == "half" and self.rot_dims:
+            order = torch.tensor(half_to_pair_order(rot, self.rot_dims))
+            uq = uq.view(H, dim + rot, -1).clone()
+            uq[:, dim:] = uq[:, dim:][:, order]
+            uq = uq.reshape(H * (dim + rot), -1)
+            if dkv is not None:
+                dkv = torch.cat([dkv[:R], dkv[R:][order]], 0)
+        parts = [w["dq"]] + ([dkv] if dkv is not None else []) + [w["g"]]
+        rows = sum(t.shape[0] for t in parts)
+        self.w_in = torch.zeros(rows + (-rows) % 8, self.D, **dev)  # zero rows up to a multiple of 8: a shape the tensor-core product takes
+        self.w_in[:rows] = torch.cat(parts, 0).to(**dev)
+        self.gate_col = rows - w["g"].shape[0]
+        self.w_uq = uq.to(**dev).contiguous()
         self.w_ukT = w["uk"].to(**dev).view(H, dim, R).transpose(1, 2).contiguous()   # [H, R, dim]: q_plain -> latent space
         self.w_uv = w["uv"].to(**dev).view(H, vdim, R).contiguous()
         self.w_ukv = torch.cat([w["uk"], w["uv"]], 0).to(**dev).contiguous()            # explicit-head form
         self.w_o = w["o"].to(**dev).contiguous()
-        self.qn, self.cn = w["qn"].to("cuda", torch.float32), w["cn"].to("cuda", torch.float32)
+        self.qn = w["qn"].to("cuda", torch.float32)
+        self.cn = w["cn"].to("cuda", torch.float32) if "cn" in w else None
         self.freq_d = self.freq.to("cuda")
+        self.score = seq_ops.ScoreOptions(H, self.window) if self.window else None
 
-    def __call__(self, h, b, store, li, prec):
+    def __call__(self, h, b, store, li, prec, resid=None, resid_scale=1.0):
         H, dim, rot, vdim, Q, R = self.H, self.dim, self.rot, self.vdim, self.Q, self.R
         T, kd = b.T, R + rot
-        pages = store.k_pages[li]
+        own = self.kv_from is None
+        pages = store.k_pages[li if own else self.kv_from]
         proj = seq_ops.linear(h, self.w_in, prec.empty(T, self.w_in.shape[0]))
         cq = prec.empty(T, Q)
-        seq_ops.latent_prepare(proj, b, self.freq_d, self.qn, self.cn, cq, pages, Q, R, rot, self.rot_dims, self.eps, PAGE)
+        seq_ops.latent_prepare(proj, b, self.freq_d, self.qn, self.cn, cq, pages if own else None, Q, R, rot, self.rot_dims, self.eps, PAGE,
+                               rot_gain=self.rot_gain)
         q = seq_ops.linear(cq, self.w_uq, prec.empty(T, H * (dim + rot))).view(T, H, dim + rot)
-        gate = proj[:, Q + R + rot:]
+        per_head = self.gate_kind == "head"
+        gate = proj[:, self.gate_col:self.gate_col + (H if per_head else H * vdim)]
         att = prec.empty(T, H, vdim)
         # rows of the lazily gathered scratch stay zero-padded to whole pages: every page a key tile touches exists
         explicit = (self.explicit_prefill and not prec.f32 and b.singles < b.E and (dim + rot, vdim) in seq_ops.MMA_HEAD_SIZES
@@ -380,19 +464,55 @@ class LatentAttention:
             # of every row: a mixed step is at most a few hundred rows)
             qlat = prec.empty(T, H, kd)
             seq_ops.linear_batched(q[:, :, :dim], self.w_ukT, qlat[:, :, :R])
-            seq_ops.rotate_heads(q[:, :, dim:], qlat[:, :, R:], b.pos, self.freq_d, self.rot_dims)
+            seq_ops.rotate_heads(q[:, :, dim:], qlat[:, :, R:], b.pos, self.freq_d, self.rot_dims, self.rot_gain)
             olat = prec.empty(T, H, R)
-            seq_ops.attn_ragged(qlat.view(T, H * kd), pages, pages, gate, olat.view(T, H * R), b, H, 1, kd, R, self.scale, 0.0, PAGE,
-                                krow=kd, vrow=kd, gate_per_head=True, only_singles=explicit)
+            seq_ops.attn_ragged(qlat.view(T, H * kd), pages, pages, gate if per_head else None, olat.view(T, H * R), b, H, 1, kd, R, self.scale, 0.0, PAGE,
+                                krow=kd, vrow=kd, gate_per_head=True, only_singles=explicit, score=self.score)
             seq_ops.linear_batched(olat, self.w_uv, att)
+            if not per_head:  # the gate has the values' width: it multiplies after the value up projection
+                seq_ops.sigmoid_gate_mul(att.view(T, H * vdim), gate)
         if explicit:
             # explicit heads for the multi-token entries (their rows of `att` are written last)
             kx, vx = seq_ops.latent_expand(pages, b, self.w_ukv, H, dim, rot, vdim, R, PAGE, prec)
             qr = q[:, :, dim:]
-            seq_ops.rotate_heads(qr, qr, b.pos, self.freq_d, self.rot_dims)
+            seq_ops.rotate_heads(qr, qr, b.pos, self.freq_d, self.rot_dims, self.rot_gain)
             seq_ops.attn_ragged(q.view(T, H * (dim + rot)), kx, vx, gate, att.view(T, H * vdim), seq_ops.dense_view(b), H, H, dim + rot, vdim,
-                                self.scale, 0.0, PAGE, gate_per_head=True, skip_singles=True)
+                                self.scale, 0.0, PAGE, gate_per_head=per_head, skip_singles=True, score=self.score)
+        if resid is not None:
+            return seq_ops.linear_add(att.view(T, H * vdim), self.w_o, resid, scale=resid_scale)
         return seq_ops.linear(att.view(T, H * vdim), self.w_o, torch.empty(T, self.D, device="cuda", dtype=torch.float32))
+
+
+class PolyNormFeedForward:
+    """W_down P(W_up h + b_up) + b_down with P(z) = a N(z) + b N(z^2) + c N(z^3) + e: powers element by element, N divides a row by its
+    root mean square (eps inside the root), (a, b, c, e) learned.  The statistics need the whole row of the up projection, so the
+    activation is a row kernel between the two products (fp32 sums over the stored activations), not a GEMM epilogue."""
+
+    def __init__(self, width, ff, eps, bias=True):
+        self.D, self.F, self.eps, self.bias = int(width), int(ff), float(eps), bool(bias)
+
+    def load(self, take, pre):
+        F, D = self.F, self.D
+        self.w = dict(up=take(pre + "up", (F, D)), down=take(pre + "down", (D, F)), act=take(pre + "act", (4,)))
+        if self.bias:
+            self.w.update(up_b=take(pre + "up.b", (F,)), down_b=take(pre + "down.b", (D,)))
+
+    def pack(self, prec):
+        w = self.w
+        f32 = dict(device="cuda", dtype=torch.float32)
+        self.w_up = w["up"].to("cuda", prec.dtype).contiguous()
+        self.w_down = w["down"].to("cuda", prec.dtype).contiguous()
+        self.coef = w["act"].to(**f32).contiguous()
+        self.b_up = w["up_b"].to(**f32).contiguous() if self.bias else None
+        self.b_down = w["down_b"].to(**f32).contiguous() if self.bias else None
+
+    def __call__(self, h, b, prec, resid=None, resid_scale=1.0):
+        T = h.shape[0]
+        z = seq_ops.linear(h, self.w_up, prec.empty(T, self.F), bias=self.b_up)
+        mid = seq_ops.polynorm(z, self.coef, z, self.eps)
+        if resid is not None:
+            return seq_ops.linear_add(mid, self.w_down, resid, bias=self.b_down, scale=resid_scale)
+        return seq_ops.linear(mid, self.w_down, torch.empty(T, self.D, device="cuda", dtype=torch.float32), bias=self.b_down)
 
 
 class SquaredReluFeedForward:

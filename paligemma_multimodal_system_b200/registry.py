@@ -63,8 +63,14 @@ def _load_kovusun(path, dtype=torch.bfloat16, **kw):
     return load_kovusun(path, dtype)
 
 
+def _load_zigivik(path, dtype=torch.bfloat16, **kw):
+    from .modeling_zigivik import load_zigivik
+    return load_zigivik(path, dtype)
+
+
 for _n in ("paligemma", "PaliGemmaForConditionalGeneration"):
     register(_n, _load_paligemma)
 register("Mapedra", _load_mapedra)
 register("Pukerax", _load_pukerax)
 register("Kovusun", _load_kovusun)
+register("Zigivik", _load_zigivik)

@@ -161,7 +161,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_N
         raise ValueError("fp32 operands produce fp32 outputs")
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == F and bias.is_contiguous()
-        _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), bias.data_ptr(), 0,
+        _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), bias.data_ptr(), 0, 1.0,
                                                 T, F, K, int(x.dtype == torch.float32), int(out.dtype == torch.float32), _lib.stream()), "pg_gemm_simt_bias")
     else:
         _lib.check(_lib.lib().pg_gemm_simt(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), T, F, K,
@@ -173,8 +173,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act: int = ACT_N
     return out
 
 
-def linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None):
-    """resid[t, f] += sum_k x[t, k] w[f, k] + bias[f]: a projection that ends in the fp32 residual stream.  bf16 operands TMA can
+def linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Optional[torch.Tensor] = None, scale: float = 1.0):
+    """resid[t, f] += (sum_k x[t, k] w[f, k] + bias[f]) * scale: a projection that ends in the fp32 residual stream.  bf16 operands TMA can
     describe: the tcgen05 kernel adds the residual in its epilogue (or red.adds split-K partials into it when there are few
     tiles); everything else: the plain-FMA kernel reads and rewrites the residual element."""
     T, K = x.shape
@@ -183,9 +183,9 @@ def linear_add(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, bias: Opti
     assert x.stride(1) == 1 and w.stride(1) == 1
     if (x.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and F % 8 == 0 and _aligned(x) and _aligned(w)
             and _aligned(resid)):
-        return _lib.gemm_residual(x, w, resid, bias=bias)
+        return _lib.gemm_residual(x, w, resid, bias=bias, scale=float(scale))
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == F and bias.is_contiguous())
-    _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), resid.data_ptr(), resid.stride(0), _lib.ptr(bias), 1,
+    _lib.check(_lib.lib().pg_gemm_simt_bias(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), resid.data_ptr(), resid.stride(0), _lib.ptr(bias), 1, float(scale),
                                             T, F, K, int(x.dtype == torch.float32), 1, _lib.stream()), "pg_gemm_simt_bias")
     return resid
 
@@ -204,6 +204,45 @@ def layernorm_shift(x, w1, b1, out1, eps, shift=None, state=None, b: "StepBatch"
                                              _lib.ptr(out2), _lib.ptr(state), *((b.pos.data_ptr(), b.row_entry.data_ptr(), b.row0.data_ptr(),
                                                                                  b.n.data_ptr(), b.slot.data_ptr()) if shift is not None else (0, 0, 0, 0, 0)),
                                              rows, D, float(eps), int(out1.dtype == torch.float32), _lib.stream()), "pg_layernorm_shift")
+
+
+def rmsnorm_conv(x, w, out_h, out_conv, eps, conv_w=None, state=None, b: "StepBatch" = None):
+    """h = x / rms(x) * w (w fp32: [D], or one number) -> out_h; out_conv = h + causal convolution of h over time per channel (conv_w fp32
+    [D, taps]; the last taps - 1 rows h of every sequence are kept in state fp32 [slots, taps - 1, D]; the batch says which rows continue which
+    sequence).  conv_w None: a bare norm.  x fp32 [rows, D]; outputs bf16 or fp32 (either may be None)."""
+    rows, D = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.float32 and w.numel() in (1, D) and w.is_contiguous()
+    outs = [o for o in (out_h, out_conv) if o is not None]
+    assert outs and all(o.is_contiguous() and o.shape == x.shape and o.dtype == outs[0].dtype for o in outs)
+    taps = 0
+    if conv_w is not None:
+        assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == D and out_conv is not None
+        taps = conv_w.shape[1]
+        if taps > 1:
+            assert state is not None and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, D)
+            assert b is not None and b.T == rows
+    ent = (b.row_entry.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.slot.data_ptr()) if taps > 1 else (0, 0, 0, 0, 0)
+    _lib.check(_lib.lib().pg_rmsnorm_conv(x.data_ptr(), w.data_ptr(), int(w.numel() == 1 and D != 1), _lib.ptr(conv_w), taps, _lib.ptr(state) if taps > 1 else 0,
+                                          _lib.ptr(out_h), _lib.ptr(out_conv), *ent, rows, D, float(eps), int(outs[0].dtype == torch.float32), _lib.stream()),
+               "pg_rmsnorm_conv")
+
+
+def polynorm(z, coef, out, eps):
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N(v) = v / sqrt(mean(v^2) + eps), (a, b, c, e) = coef (fp32 [4], device)."""
+    rows, F = z.shape
+    assert z.dtype == out.dtype and out.shape == z.shape and z.stride(1) == 1 and out.stride(1) == 1 and coef.dtype == torch.float32 and coef.numel() == 4
+    _lib.check(_lib.lib().pg_polynorm(z.data_ptr(), z.stride(0), coef.data_ptr(), out.data_ptr(), out.stride(0), rows, F, float(eps),
+                                      int(z.dtype == torch.float32), _lib.stream()), "pg_polynorm")
+    return out
+
+
+def sigmoid_gate_mul(y, gate):
+    """y[t, c] *= sigmoid(gate[t, c]) in place (one type; any row pitch)."""
+    rows, n = y.shape
+    assert gate.shape == y.shape and gate.dtype == y.dtype and y.stride(1) == 1 and gate.stride(1) == 1
+    _lib.check(_lib.lib().pg_sigmoid_gate_mul(y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), rows, n, int(y.dtype == torch.float32),
+                                              _lib.stream()), "pg_sigmoid_gate_mul")
+    return y
 
 
 GLU_SILU, GLU_CLAMPED = 1, 2
@@ -257,15 +296,17 @@ def side_gate(z, tokens, table, col0, out, n):
                                        out.stride(0), rows, int(n), n_pad, int(out.dtype == torch.float32), _lib.stream()), "pg_side_gate")
 
 
-def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_pages, H, G, dim, vdim, rot_dims, eps, page, norm_qk=True, norm_v=True):
+def attn_prepare(qkv, b: StepBatch, freq, q_norm, k_norm, q_out, k_pages, v_pages, H, G, dim, vdim, rot_dims, eps, page, norm_qk=True, norm_v=True,
+                 v_from_k=False):
     """q_norm / k_norm None: norms without a weight; norm_qk / norm_v False: no q/k norm / no value norm; k_pages and v_pages None: the
-    rows hold queries only (the layer attends over another layer's cache)."""
+    rows hold queries only (the layer attends over another layer's cache); v_from_k: the rows have no value columns, the values are the
+    keys as projected (before norm and rotation)."""
     assert qkv.stride(1) == 1 and freq.dtype == torch.float64 and qkv.dtype == q_out.dtype and (k_pages is None) == (v_pages is None)
     assert k_pages is None or k_pages.dtype == qkv.dtype
     _lib.check(_lib.lib().pg_attn_prepare(qkv.data_ptr(), qkv.stride(0), b.pos.data_ptr(), b.row_entry.data_ptr(), b.page_table.data_ptr(),
                                           b.max_pages, page, freq.data_ptr(), _lib.ptr(q_norm), _lib.ptr(k_norm), q_out.data_ptr(),
                                           _lib.ptr(k_pages), _lib.ptr(v_pages), b.T, H, G, dim, vdim, rot_dims, float(eps), int(bool(norm_qk)),
-                                          int(bool(norm_v)), int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
+                                          int(bool(norm_v)), int(bool(v_from_k)), int(qkv.dtype == torch.float32), _lib.stream()), "pg_attn_prepare")
 
 
 class ScoreOptions:
@@ -414,22 +455,23 @@ def linear_batched(x, w, out):
     return out
 
 
-def latent_prepare(proj, b: StepBatch, freq, q_norm, c_norm, cq_out, pages, q_rank, rank, rot, rot_dims, eps, page):
-    assert proj.stride(1) == 1 and freq.dtype == torch.float64 and pages.dtype == proj.dtype and pages.shape[-1] == rank + rot
+def latent_prepare(proj, b: StepBatch, freq, q_norm, c_norm, cq_out, pages, q_rank, rank, rot, rot_dims, eps, page, rot_gain=1.0):
+    """pages None: the layer reads another layer's cached rows; only the normalised query latent is made."""
+    assert proj.stride(1) == 1 and freq.dtype == torch.float64 and (pages is None or (pages.dtype == proj.dtype and pages.shape[-1] == rank + rot))
     assert cq_out is None or (cq_out.dtype == proj.dtype and cq_out.is_contiguous())
     _lib.check(_lib.lib().pg_latent_prepare(proj.data_ptr(), proj.stride(0), b.pos.data_ptr(), b.row_entry.data_ptr(), b.page_table.data_ptr(),
-                                            b.max_pages, page, freq.data_ptr(), _lib.ptr(q_norm), c_norm.data_ptr(), _lib.ptr(cq_out), pages.data_ptr(),
-                                            b.T, q_rank, rank, rot, rot_dims, float(eps), int(proj.dtype == torch.float32), _lib.stream()),
+                                            b.max_pages, page, freq.data_ptr(), _lib.ptr(q_norm), _lib.ptr(c_norm), _lib.ptr(cq_out), _lib.ptr(pages),
+                                            b.T, q_rank, rank, rot, rot_dims, float(eps), float(rot_gain), int(proj.dtype == torch.float32), _lib.stream()),
                "pg_latent_prepare")
 
 
-def rotate_heads(src, dst, pos, freq, rot_dims):
+def rotate_heads(src, dst, pos, freq, rot_dims, rot_gain=1.0):
     """src, dst: [T, H, n] views (unit last stride, any row / head pitch) of one type; the first rot_dims of every head vector are
-    rotated in interleaved pairs by pos[t] * freq[i]."""
+    rotated in interleaved pairs by pos[t] * freq[i]; rot_gain multiplies cosines and sines."""
     T, H, n = src.shape
     assert dst.shape == src.shape and src.dtype == dst.dtype and src.stride(2) == 1 and dst.stride(2) == 1
     _lib.check(_lib.lib().pg_rotate_heads(src.data_ptr(), src.stride(0), src.stride(1), dst.data_ptr(), dst.stride(0), dst.stride(1), pos.data_ptr(),
-                                          freq.data_ptr(), T, H, n, rot_dims, int(src.dtype == torch.float32), _lib.stream()), "pg_rotate_heads")
+                                          freq.data_ptr(), T, H, n, rot_dims, float(rot_gain), int(src.dtype == torch.float32), _lib.stream()), "pg_rotate_heads")
 
 
 def latent_expand(pages, b: StepBatch, w_ukv, H, dim, rot, vdim, rank, page, prec):
