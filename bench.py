@@ -392,7 +392,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the cfg2 / cfg4 / cfg5 / strong-scaling measurements")
     # --arch mapedra: the Mapedra decoder beside the Gemma decoder at equal layer sizes (paligemma_multimodal_system_b200/bench_seq.py);
     # the default (paligemma) workload and its JSON line are untouched by these flags
-    ap.add_argument("--arch", default="paligemma", choices=["paligemma", "mapedra", "pukerax", "kovusun"])
+    ap.add_argument("--arch", default="paligemma", choices=["paligemma", "mapedra", "pukerax", "kovusun", "zigivik"])
     ap.add_argument("--width", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
@@ -414,6 +414,9 @@ def main():
     if args.arch == "kovusun":  # the Kovusun decoder beside the Mapedra decoder at equal layer sizes (--head-dim 64)
         from paligemma_multimodal_system_b200 import bench_seq
         return bench_seq.run_kovusun(args)
+    if args.arch == "zigivik":  # the Zigivik decoder beside the Kovusun decoder with dense feed-forwards at equal layer sizes (--head-dim 64)
+        from paligemma_multimodal_system_b200 import bench_seq
+        return bench_seq.run_zigivik(args)
 
     from paligemma_multimodal_system_b200.random_init import make_inputs, paligemma_3b_config
     cfg = paligemma_3b_config(args.image_size)

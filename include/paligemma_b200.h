@@ -307,16 +307,17 @@ int pg_gemm_simt_bias(const void* x, long long ldx, const void* w, long long ldw
 
 /* ---- normalised residual read through a short causal convolution; polynomial-of-norms activation ------------------------------
  * pg_rmsnorm_conv: h[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w (w: fp32 [D], or ONE number when w_scalar != 0); out_h[t] = h[t];
- *   out_conv[t, c] = h[t, c] + sum_{j < taps} conv_w[c * taps + j] * h[t - taps + 1 + j, c], where rows before the sequence's
+ *   out_conv[t, c] = h[t, c] + sum_{j < taps} conv_w[j * D + c] * h[t - taps + 1 + j, c] (conv_w tap-major: fp32 [taps, D]), where rows before the sequence's
  *   start are zeros and rows before this step come from state (fp32 [slots, taps - 1, D]: the last taps - 1 rows h of the
  *   sequence in slot entry_slot[e], oldest first; ignored when entry_ctx[e] == 0; rewritten here).  conv_w NULL: no convolution,
- *   no state (a bare norm; out_conv, when given, equals out_h).  Either output may be NULL.  taps <= 8.
+ *   no state (a bare norm; out_conv, when given, equals out_h).  Either output may be NULL.  taps <= 8.  entries = number of entries
+ *   of the step (0: unknown; steps of thousands of rows then stay on the one-CTA-per-row kernel).
  * pg_polynorm: out[t, f] = a N(z)[f] + b N(z^2)[f] + c N(z^3)[f] + e with (a, b, c, e) = coef[0..3] (fp32, device), powers taken
  *   element by element and N(v) = v / sqrt(mean_f(v^2) + eps); z and out in the activation type, statistics fp32.
  * pg_sigmoid_gate_mul: y[t, c] *= sigmoid(gate[t, c]) for c < n (both in the activation type, pitches ldy / ldg). */
 int pg_rmsnorm_conv(const float* x, const float* w, int w_scalar, const float* conv_w, int taps, float* state, void* out_h, void* out_conv,
-                    const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* entry_slot, int rows, int D,
-                    float eps, int out_f32, void* stream);
+                    const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* entry_slot, int rows, int entries,
+                    int D, float eps, int out_f32, void* stream);
 int pg_polynorm(const void* z, long long ldz, const float* coef, void* out, long long ldo, int rows, int F, float eps, int act_f32, void* stream);
 int pg_sigmoid_gate_mul(void* y, long long ldy, const void* gate, long long ldg, int rows, int n, int act_f32, void* stream);
 

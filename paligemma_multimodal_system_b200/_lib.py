@@ -94,7 +94,7 @@ SIGNATURES = {
     "pg_moe_dense_runs": [p, i64, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p],
     "pg_moe_combine": [p, i64, p, p, p, p, i64, p, i64, p, i32, i32, i32, i32, p, i64, i32, p],
     "pg_gemm_simt_bias": [p, i64, p, i64, p, i64, p, i32, f32, i32, i32, i32, i32, i32, p],
-    "pg_rmsnorm_conv": [p, p, i32, p, i32, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],
+    "pg_rmsnorm_conv": [p, p, i32, p, i32, p, p, p, p, p, p, p, p, i32, i32, i32, f32, i32, p],
     "pg_polynorm": [p, i64, p, p, i64, i32, i32, f32, i32, p],
     "pg_sigmoid_gate_mul": [p, i64, p, i64, i32, i32, i32, p],
     "pg_layernorm_shift": [p, p, p, p, p, p, p, p, p, p, p, p, p, p, i32, i32, f32, i32, p],

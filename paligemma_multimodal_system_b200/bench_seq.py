@@ -650,3 +650,169 @@ def run_kovusun(args):
             out[key] = round(out[key], 1)
     print(json.dumps(out), flush=True)
     return out
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# `bench.py --arch zigivik`: the Zigivik decoder beside the Kovusun decoder with dense feed-forwards on every layer (the closest model
+# of the package: parallel layers behind one norm kernel with a per-sequence state, windowed attention over pages, a feed-forward with
+# biases that ends in the residual) at equal width / heads / k/v heads / feed-forward / depth
+# ----------------------------------------------------------------------------------------------------------------------
+def zigivik_config(width, heads, kv_heads, dim, ff, vocab, layers, taps=4):
+    """Layer types in turn: latent attention (window 1024; 64 + 32-wide keys, 64-wide values, ranks width / 2 and width / 4), two layers of
+    grouped attention whose keys are the values, and a latent layer that borrows the first one's cached rows (window 512)."""
+    lat = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": width // 2, "kv_rank": width // 4, "scale": (dim + dim // 2) ** -0.5,
+           "rot": {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 2.5e5, "dims": dim}}
+    ls = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            m = {"type": "latent_attention", "mixer": dict(lat, mask={"size": 1024})}
+        elif k == 3:
+            m = {"type": "latent_attention", "mixer": dict(lat, mask={"size": 512}, kv_from=i - 3)}
+        else:
+            m = {"type": "attention", "mixer": dict(att)}
+        ls.append(dict(m, mlp={"kind": "dense", "ff": ff}))
+    return {"architecture": "Zigivik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": taps}, "residual_mult": 0.5, "layers": ls}
+
+
+def random_zigivik(cfg, seed=0):
+    from .modeling_zigivik import ZigivikConfig, ZigivikForCausalLM
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    c = ZigivikConfig(cfg)
+    model = ZigivikForCausalLM(c, torch.bfloat16)
+
+    def take(name, shape):
+        r = torch.randn(tuple(shape), device="cuda", generator=g)
+        if name.endswith(("norm1", ".norm")):
+            t = 1.0 + 0.05 * r
+        elif name.endswith(".b"):
+            t = 0.1 * r
+        elif name.endswith("canon1"):
+            t = 0.2 * r
+        elif name.endswith("act"):
+            t = torch.tensor([0.6, 0.3, 0.2, 0.05], device="cuda")
+        else:
+            t = r * shape[-1] ** -0.5
+        return t.to(torch.bfloat16)
+
+    model.embed, model.embed_norm = take("embed", (c.vocab, c.width)), take("embed.norm", ())
+    for blk in model.blocks:
+        blk.load(take)
+    model.final_norm, model.head = take("final.norm", ()), take("head", (c.vocab, c.width))
+    model.pack()
+    return model
+
+
+def kovusun_dense_config(width, heads, kv_heads, dim, ff, vocab, layers):
+    cfg = kovusun_config(width, heads, kv_heads, dim, ff, vocab, layers)
+    for l in cfg["layers"]:
+        l["mlp"] = {"kind": "dense", "ff": ff, "limit": 7.0}
+    return cfg
+
+
+def run_zigivik(args):
+    _lib.require_device()
+    torch.cuda.set_device(0)
+    hbm, tflops, src = peaks()
+    W, H, G, dh, F, V, L = args.width, args.heads, args.kv_heads, args.head_dim, args.ff, args.vocab, args.layers
+    B_pre, S, B_dec, ctx = args.prefill_batch, args.seq_len, args.decode_batch, args.context
+    flush = torch.zeros(64 * 1024 * 1024, device="cuda", dtype=torch.float32)  # 256 MB > L2
+    cfg = zigivik_config(W, H, G, dh, F, V, L)
+    out = {"metric": "zigivik_vs_kovusun_tokens_per_s", "dtype": "bf16", "data": "synthetic", "peaks": src,
+           "config": {"width": W, "heads": H, "kv_heads": G, "head_dim": dh, "ff": F, "vocab": V, "layers": L, "taps": cfg["canon"]["taps"],
+                      "latent": {k: cfg["layers"][0]["mixer"][k] for k in ("dim", "rot_dim", "vdim", "q_rank", "kv_rank")},
+                      "windows": [(l["mixer"].get("mask") or {}).get("size") for l in cfg["layers"][:4]],
+                      "prefill": [B_pre, S], "decode": [B_dec, ctx], "l2": "256 MB buffer rewritten before every timed launch"}}
+    model = random_zigivik(cfg)
+    eng = _throughput(model, args, flush, V, "zigivik", out)
+    prec, k, store = model.prec, {}, eng.store
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        blk0 = model.blocks[0]
+        x, h, hc = torch.randn(T, W, device="cuda"), prec.empty(T, W), prec.empty(T, W)
+        k[f"norm_convolution_{name}"] = dict(s=timed(lambda: seq_ops.rmsnorm_conv(x, blk0.norm1_d, h, hc, 1e-6, conv_w=blk0.canon_d, state=store.state[L], b=b),
+                                                     flush=flush), bytes=T * W * (4 + 2 + 2))
+        z = torch.randn(T, F, device="cuda").to(torch.bfloat16)
+        k[f"polynomial_of_norms_{name}"] = dict(s=timed(lambda: seq_ops.polynorm(z, blk0.ff.coef, z, 1e-6), flush=flush), bytes=T * F * (2 + 2))
+        hin = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+        k[f"feed_forward_{name}"] = dict(s=timed(lambda: blk0.ff(hin, b, prec, resid=x, resid_scale=0.5), flush=flush), flops=4 * T * W * F,
+                                         bytes=2 * W * F * 2 + T * (W * 2 + F * 6 + W * 8))
+        for li, blk in enumerate(model.blocks[:4]):
+            mx = blk.mixer
+            if li == 2:
+                continue  # the same kind as layer 1
+            tag = cfg["layers"][li]["type"] + ("_borrowed" if mx.kv_from is not None else "")
+            src_li = li if mx.kv_from is None else mx.kv_from
+            store.k_pages[src_li].normal_()
+            if store.v_pages[src_li] is not None:
+                store.v_pages[src_li].normal_()
+            win = mx.window or (c0 + n_new)
+            pairs = n_seq * sum(min(i + 1, win) for i in range(c0, c0 + n_new))
+            if tag.startswith("latent"):
+                kd, R = mx.R + mx.rot, mx.R
+                wts = (mx.w_in.numel() + mx.w_uq.numel() + mx.w_ukv.numel() + mx.w_o.numel()) * 2
+                # explicit heads for prompt portions, absorbed heads for decoded tokens
+                fl = 2 * T * W * mx.w_in.shape[0] + 2 * T * mx.Q * H * (dh + mx.rot) + 2 * T * H * dh * W
+                fl += (4 * H * (dh + mx.rot // 2) * pairs + 2 * n_seq * (c0 + n_new) * R * H * 2 * dh) if n_new > 1 else (2 * H * (kd + R) * pairs + 4 * T * H * dh * R)
+                by = wts + n_seq * min(c0 + n_new, win + n_new) * kd * 2 + T * W * (2 + 8)
+            else:
+                wts = (mx.w_in.numel() + mx.w_o.numel()) * 2
+                fl = 2 * T * W * mx.w_in.shape[0] + 2 * T * H * dh * W + 4 * dh * H * pairs
+                by = wts + n_seq * (c0 + n_new) * G * 2 * dh * 2 + T * W * (2 + 8)
+            k[f"mixer_{tag}_{name}"] = dict(s=timed(lambda: mx(hin, b, store, li, prec, resid=x, resid_scale=0.5), flush=flush), flops=fl, bytes=by)
+        for i in range(n_seq):
+            store.release(("k", i))
+    del eng, model, store
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- Kovusun with dense feed-forwards at equal size
+    kc = kovusun_dense_config(W, H, G, dh, F, V, L)
+    km = random_kovusun(kc)
+    eng = _throughput(km, args, flush, V, "kovusun", out)
+    store, prec = eng.store, km.prec
+    for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
+        b = _entries(store, n_seq, n_new, c0)
+        T = b.T
+        blk0 = km.blocks[0]
+        x, a1, a2 = torch.randn(T, W, device="cuda"), prec.empty(T, W), prec.empty(T, W)
+        k[f"kovusun_two_norms_shift_{name}"] = dict(
+            s=timed(lambda: seq_ops.layernorm_shift(x, blk0.norm1_d, blk0.norm1_bd, a1, 1e-5, shift=blk0.shift_d, state=store.state[L], b=b, w2=blk0.norm2_d,
+                                                    b2=blk0.norm2_bd, out2=a2), flush=flush), bytes=T * W * (4 + 2 + 2))
+        hin = torch.randn(T, W, device="cuda").to(torch.bfloat16)
+        k[f"kovusun_clamped_glu_feed_forward_{name}"] = dict(s=timed(lambda: blk0.ff(hin, b, prec, resid=x), flush=flush), flops=6 * T * W * F,
+                                                             bytes=3 * W * F * 2 + T * (W * 2 + F * 4 + W * 8))
+        gu = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
+        mid = prec.empty(T, F)
+        k[f"kovusun_gated_unit_unfused_{name}"] = dict(s=timed(lambda: seq_ops.glu(gu, mid, seq_ops.GLU_CLAMPED, 7.0, 1.702), flush=flush), bytes=T * F * (4 + 2))
+        for li in (0, 1):
+            mx = km.blocks[li].mixer
+            store.k_pages[li].normal_()
+            store.v_pages[li].normal_()
+            win = mx.window or (c0 + n_new)
+            pairs = n_seq * sum(min(i + 1, win) + max(0, min(mx.keep_first, i + 1 - win)) for i in range(c0, c0 + n_new))
+            wts = (mx.w_in.numel() + mx.w_o.numel()) * 2
+            k[f"kovusun_mixer_{kc['layers'][li]['type']}_{name}"] = dict(
+                s=timed(lambda: mx(hin, b, store, li, prec, resid=x), flush=flush), flops=2 * T * W * mx.w_in.shape[0] + 2 * T * H * dh * W + 4 * dh * H * pairs,
+                bytes=wts + n_seq * min(c0 + n_new, win + mx.keep_first + n_new) * G * 2 * dh * 2 + T * W * (2 + 8))
+        for i in range(n_seq):
+            store.release(("k", i))
+    for name, d in k.items():
+        d["us"] = round(d.pop("s") * 1e6, 2)
+        d["hbm_frac"] = round(d["bytes"] / (d["us"] * 1e-6) / hbm, 4)
+        if "flops" in d:
+            d["tflops"] = round(d["flops"] / (d["us"] * 1e-6) / 1e12, 2)
+            d["tensor_frac"] = round(d["flops"] / (d["us"] * 1e-6) / tflops, 5)
+        # distance from the roofline: the measured time over the larger of the two bounds
+        bound = max(d["bytes"] / hbm, d.get("flops", 0) / tflops)
+        d["x_roofline"] = round(d["us"] * 1e-6 / bound, 2)
+    out["kernels"] = k
+    out["value"] = out["zigivik_decode_tok_s"]
+    out["unit"] = "tokens/s"
+    out["n_gpus"] = 1
+    for key in list(out):
+        if key.endswith("tok_s"):
+            out[key] = round(out[key], 1)
+    print(json.dumps(out), flush=True)
+    return out

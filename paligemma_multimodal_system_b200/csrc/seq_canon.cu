@@ -1,7 +1,7 @@
 // Row kernels of decoders whose mixer reads the normalised residual through a short causal convolution over time:
 //
 //   pg_rmsnorm_conv     h = x / sqrt(mean(x^2) + eps) * g (g: one weight per channel, or ONE number for the whole row);
-//                       out_h[t] = h[t] (what a feed-forward beside the mixer reads), out_conv[t] = h[t] + sum_j cw[:, j] h[t - taps + 1 + j]
+//                       out_h[t] = h[t] (what a feed-forward beside the mixer reads), out_conv[t] = h[t] + sum_j cw[j, :] h[t - taps + 1 + j]
 //                       per channel, zeros before the sequence's start.  The last taps - 1 rows h of a sequence live in an fp32
 //                       state slot, so a portion or a decoded token continues where the sequence stopped.
 //   pg_polynorm         out = a N(z) + b N(z^2) + c N(z^3) + e with N(v) = v / sqrt(mean(v^2) + eps) over the row (powers element-wise)
@@ -62,14 +62,16 @@ __global__ void __launch_bounds__(256) rmsnorm_conv_kernel(const float* __restri
                                                            const float* __restrict__ cw, int taps, float* __restrict__ state,
                                                            TO* __restrict__ out_h, TO* __restrict__ out_conv, const int* __restrict__ row_entry,
                                                            const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
-                                                           const int* __restrict__ entry_ctx, const int* __restrict__ entry_slot, int D, float eps) {
+                                                           const int* __restrict__ entry_ctx, const int* __restrict__ entry_slot, int D, float eps,
+                                                           int by_entry) {
   __shared__ float red[8];
   __shared__ float inv[2 * MAX_K + 1];
-  const long long t = blockIdx.x;
   const int K = cw != nullptr ? taps - 1 : 0;
+  // by_entry: one CTA per entry, for its first rows and its slot only (the other rows belong to the row-chunk kernel)
+  const long long t = by_entry ? entry_row0[blockIdx.x] : blockIdx.x;
   int i = 0, ne = 1, e = 0;
   if (K > 0) {
-    e = row_entry[t];
+    e = by_entry ? (int)blockIdx.x : row_entry[t];
     i = (int)(t - entry_row0[e]);
     ne = entry_n[e];
     if (i > 0 && i < K) return;
@@ -87,8 +89,8 @@ __global__ void __launch_bounds__(256) rmsnorm_conv_kernel(const float* __restri
       if (out_conv != nullptr) {
         float acc = hv;
         if (cw != nullptr) {
-          acc = fmaf(cw[(long long)d * taps + K], hv, acc);
-          for (int j = 0; j < K; ++j) acc = fmaf(cw[(long long)d * taps + j], x[(t - K + j) * D + d] * inv[j] * g, acc);
+          acc = fmaf(cw[(long long)K * D + d], hv, acc);
+          for (int j = 0; j < K; ++j) acc = fmaf(cw[(long long)j * D + d], x[(t - K + j) * D + d] * inv[j] * g, acc);
         }
         st_a(out_conv, t * D + d, acc);
       }
@@ -129,7 +131,7 @@ __global__ void __launch_bounds__(256) rmsnorm_conv_kernel(const float* __restri
                 if (src == q) v = hf[q];
                 if (K + src == q && src < 0) v = old[q];
               }
-              acc = fmaf(cw[(long long)d * taps + j], v, acc);
+              acc = fmaf(cw[(long long)j * D + d], v, acc);
             }
           }
           st_a(out_conv, (t + r) * D + d, acc);
@@ -154,6 +156,63 @@ __global__ void __launch_bounds__(256) rmsnorm_conv_kernel(const float* __restri
         }
         slot[(long long)k * D + d] = v;
       }
+    }
+  }
+}
+
+// Prompt portions: one CTA per chunk of RC consecutive rows.  Pass 1: a warp per row (the chunk and the taps - 1 rows before it) leaves
+// 1 / rms in shared memory.  Pass 2: a thread owns four channels and walks down the chunk's rows; the earlier rows it needs are the
+// ones it read in its last iterations (L1).  Rows less than taps - 1 tokens
+// into their entry are left to the per-entry launch of the kernel above (they need the state slot).
+__device__ __forceinline__ void st_a4(float* p, long long i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void st_a4(bf16* p, long long i, float4 v) {
+  uint2 u;
+  u.x = pg::pack_bf16(v.x, v.y);
+  u.y = pg::pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(p + i) = u;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_conv_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, int w_stride,
+                                                                const float* __restrict__ cw, int taps, TO* __restrict__ out_h,
+                                                                TO* __restrict__ out_conv, const int* __restrict__ row_entry,
+                                                                const int* __restrict__ entry_row0, int rows, int RC, int D, float eps) {
+  __shared__ float inv[32 + MAX_K];
+  __shared__ int into[32];  // rows into their entry
+  const int K = taps - 1;
+  const int r0 = blockIdx.x * RC, nr = min(RC, rows - r0);
+  const int first = max(r0 - K, 0), nh = r0 - first, total = nh + nr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int r = threadIdx.x; r < nr; r += 256) into[r] = r0 + r - entry_row0[row_entry[r0 + r]];
+  for (int rr = warp; rr < total; rr += 8) {
+    const float4* x4 = reinterpret_cast<const float4*>(x + (long long)(first + rr) * D);
+    float s = 0.f;
+    for (int i = lane; i < D / 4; i += 32) { const float4 v = x4[i]; s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s)))); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) inv[rr] = 1.0f / sqrtf(s / (float)D + eps);
+  }
+  __syncthreads();
+  for (int c4 = threadIdx.x; c4 < D / 4; c4 += 256) {
+    const int c = 4 * c4;
+    float4 g;
+    if (w_stride) g = *reinterpret_cast<const float4*>(w + c);
+    else g.x = g.y = g.z = g.w = w[0];
+    for (int r = 0; r < nr; ++r) {
+      if (into[r] < K) continue;  // needs the state slot
+      const long long t = r0 + r;
+      float4 hv, acc;
+      for (int j = 0; j <= K; ++j) {
+        const float4 xv = *reinterpret_cast<const float4*>(x + (t - K + j) * D + c);
+        const float iv = inv[nh + r - K + j];
+        const float4 cj = *reinterpret_cast<const float4*>(cw + (long long)j * D + c);
+        const float4 hj = make_float4(xv.x * iv * g.x, xv.y * iv * g.y, xv.z * iv * g.z, xv.w * iv * g.w);
+        if (j == 0) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        acc.x = fmaf(cj.x, hj.x, acc.x); acc.y = fmaf(cj.y, hj.y, acc.y); acc.z = fmaf(cj.z, hj.z, acc.z); acc.w = fmaf(cj.w, hj.w, acc.w);
+        if (j == K) hv = hj;
+      }
+      if (out_h != nullptr) st_a4(out_h, t * D + c, hv);
+      st_a4(out_conv, t * D + c, make_float4(hv.x + acc.x, hv.y + acc.y, hv.z + acc.z, hv.w + acc.w));
     }
   }
 }
@@ -183,6 +242,57 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const TA* z, long long ld
   }
 }
 
+// The same with 16-byte accesses, eight elements per thread and step (F and the pitches multiples of 8, 16-byte aligned rows).
+__device__ __forceinline__ void ld8(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const bf16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t q[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(q[i] << 16); v[2 * i + 1] = __uint_as_float(q[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ void st8(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void st8(bf16* p, const float* v) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pg::pack_bf16(v[0], v[1]), pg::pack_bf16(v[2], v[3]), pg::pack_bf16(v[4], v[5]), pg::pack_bf16(v[6], v[7]));
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256) polynorm_vec_kernel(const TA* z, long long ldz, const float* __restrict__ coef, TA* out, long long ldo, int F,
+                                                           float eps) {
+  __shared__ float red[8];
+  const long long t = blockIdx.x;
+  const TA* zr = z + t * ldz;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int f = 8 * threadIdx.x; f < F; f += 8 * 256) {
+    float v[8];
+    ld8(zr + f, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float v2 = v[i] * v[i], v4 = v2 * v2;
+      s2 += v2;
+      s4 += v4;
+      s6 = fmaf(v4, v2, s6);
+    }
+  }
+  s2 = block_sum(s2, red);
+  s4 = block_sum(s4, red);
+  s6 = block_sum(s6, red);
+  const float a = coef[0] / sqrtf(s2 / (float)F + eps), b = coef[1] / sqrtf(s4 / (float)F + eps), c = coef[2] / sqrtf(s6 / (float)F + eps);
+  const float e = coef[3];
+  for (int f = 8 * threadIdx.x; f < F; f += 8 * 256) {
+    float v[8];
+    ld8(zr + f, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fmaf(v[i], fmaf(v[i], fmaf(v[i], c, b), a), e);
+    st8(out + t * ldo + f, v);
+  }
+}
+
 template <typename TA>
 __global__ void sigmoid_gate_mul_kernel(TA* __restrict__ y, long long ldy, const TA* __restrict__ gate, long long ldg, int n, long long total) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -197,7 +307,7 @@ __global__ void sigmoid_gate_mul_kernel(TA* __restrict__ y, long long ldy, const
 
 extern "C" int pg_rmsnorm_conv(const float* x, const float* w, int w_scalar, const float* conv_w, int taps, float* state, void* out_h, void* out_conv,
                                const int* row_entry, const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* entry_slot, int rows,
-                               int D, float eps, int out_f32, void* stream) {
+                               int entries, int D, float eps, int out_f32, void* stream) {
   if (rows <= 0 || D <= 0 || x == nullptr || w == nullptr || (out_h == nullptr && out_conv == nullptr)) return PG_ERR_ARG;
   if (conv_w != nullptr) {
     if (taps < 1 || taps - 1 > MAX_K || out_conv == nullptr) return PG_ERR_ARG;
@@ -206,18 +316,42 @@ extern "C" int pg_rmsnorm_conv(const float* x, const float* w, int w_scalar, con
   }
   cudaStream_t st = PG_ST(stream);
   const int ws = w_scalar ? 0 : 1;
+  // prompt portions: chunks of consecutive rows, about two waves of four CTAs per SM; the entries' first rows and slots in a launch of their own
+  const int RC = min(32, (rows + 8 * pg::num_sms() - 1) / (8 * pg::num_sms()));
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (conv_w != nullptr && taps > 1 && entries > 0 && RC >= 2 && D % 4 == 0 && al16(x) && al16(w) && al16(conv_w) && al16(out_h) && al16(out_conv)) {
+    const int chunks = (rows + RC - 1) / RC;
+    if (out_f32) {
+      rmsnorm_conv_rows_kernel<float><<<chunks, 256, 0, st>>>(x, w, ws, conv_w, taps, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry, entry_row0, rows, RC, D, eps);
+      rmsnorm_conv_kernel<float><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry,
+                                                          entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
+    } else {
+      rmsnorm_conv_rows_kernel<bf16><<<chunks, 256, 0, st>>>(x, w, ws, conv_w, taps, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry, entry_row0, rows, RC, D, eps);
+      rmsnorm_conv_kernel<bf16><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry,
+                                                         entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
+    }
+    pg_count_launch(1);
+    PG_RET();
+  }
   if (out_f32)
     rmsnorm_conv_kernel<float><<<rows, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry,
-                                                     entry_row0, entry_n, entry_ctx, entry_slot, D, eps);
+                                                     entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 0);
   else
     rmsnorm_conv_kernel<bf16><<<rows, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry,
-                                                    entry_row0, entry_n, entry_ctx, entry_slot, D, eps);
+                                                    entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 0);
   PG_RET();
 }
 
 extern "C" int pg_polynorm(const void* z, long long ldz, const float* coef, void* out, long long ldo, int rows, int F, float eps, int act_f32,
                            void* stream) {
   if (rows <= 0 || F <= 0 || z == nullptr || coef == nullptr || out == nullptr) return PG_ERR_ARG;
+  if (F % 8 == 0 && ldz % 8 == 0 && ldo % 8 == 0 && ((reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    if (act_f32)
+      polynorm_vec_kernel<float><<<rows, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(z), ldz, coef, static_cast<float*>(out), ldo, F, eps);
+    else
+      polynorm_vec_kernel<bf16><<<rows, 256, 0, PG_ST(stream)>>>(static_cast<const bf16*>(z), ldz, coef, static_cast<bf16*>(out), ldo, F, eps);
+    PG_RET();
+  }
   if (act_f32)
     polynorm_kernel<float><<<rows, 256, 0, PG_ST(stream)>>>(static_cast<const float*>(z), ldz, coef, static_cast<float*>(out), ldo, F, eps);
   else

@@ -99,7 +99,7 @@ class ZigivikBlock:
     def pack(self, prec):
         f32 = dict(device="cuda", dtype=torch.float32)
         self.norm1_d = self.norm1.to(**f32).reshape(1).contiguous()
-        self.canon_d = self.canon.to(**f32).contiguous() if self.canon is not None else None
+        self.canon_d = self.canon.to(**f32).t().contiguous() if self.canon is not None else None  # tap-major: the kernels read a tap's weights as a row
         self.mixer.pack(prec)
         if self.ff is not None:
             self.ff.pack(prec)

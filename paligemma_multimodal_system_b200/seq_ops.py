@@ -208,7 +208,7 @@ def layernorm_shift(x, w1, b1, out1, eps, shift=None, state=None, b: "StepBatch"
 
 def rmsnorm_conv(x, w, out_h, out_conv, eps, conv_w=None, state=None, b: "StepBatch" = None):
     """h = x / rms(x) * w (w fp32: [D], or one number) -> out_h; out_conv = h + causal convolution of h over time per channel (conv_w fp32
-    [D, taps]; the last taps - 1 rows h of every sequence are kept in state fp32 [slots, taps - 1, D]; the batch says which rows continue which
+    [taps, D], tap-major, the oldest tap first; the last taps - 1 rows h of every sequence are kept in state fp32 [slots, taps - 1, D]; the batch says which rows continue which
     sequence).  conv_w None: a bare norm.  x fp32 [rows, D]; outputs bf16 or fp32 (either may be None)."""
     rows, D = x.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and w.dtype == torch.float32 and w.numel() in (1, D) and w.is_contiguous()
@@ -216,14 +216,14 @@ def rmsnorm_conv(x, w, out_h, out_conv, eps, conv_w=None, state=None, b: "StepBa
     assert outs and all(o.is_contiguous() and o.shape == x.shape and o.dtype == outs[0].dtype for o in outs)
     taps = 0
     if conv_w is not None:
-        assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == D and out_conv is not None
-        taps = conv_w.shape[1]
+        assert conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[1] == D and out_conv is not None
+        taps = conv_w.shape[0]
         if taps > 1:
             assert state is not None and state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, D)
             assert b is not None and b.T == rows
     ent = (b.row_entry.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.ctx.data_ptr(), b.slot.data_ptr()) if taps > 1 else (0, 0, 0, 0, 0)
     _lib.check(_lib.lib().pg_rmsnorm_conv(x.data_ptr(), w.data_ptr(), int(w.numel() == 1 and D != 1), _lib.ptr(conv_w), taps, _lib.ptr(state) if taps > 1 else 0,
-                                          _lib.ptr(out_h), _lib.ptr(out_conv), *ent, rows, D, float(eps), int(outs[0].dtype == torch.float32), _lib.stream()),
+                                          _lib.ptr(out_h), _lib.ptr(out_conv), *ent, rows, b.E if taps > 1 else 0, D, float(eps), int(outs[0].dtype == torch.float32), _lib.stream()),
                "pg_rmsnorm_conv")
 
 

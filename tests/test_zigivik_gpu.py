@@ -172,7 +172,7 @@ def test_norm_and_causal_convolution_in_portions(D, taps, scalar, f32):
         b = seq_ops.make_step_batch(es)
         x = torch.cat([xs[i][fed[i]:fed[i] + k] for i, k in rows]).cuda().contiguous()
         oh, oc = torch.empty(b.T, D, device="cuda", dtype=dt), torch.empty(b.T, D, device="cuda", dtype=dt)
-        seq_ops.rmsnorm_conv(x, wn.reshape(-1).cuda().contiguous(), oh, oc, eps, conv_w=cw.cuda().contiguous(), state=store.state[0], b=b)
+        seq_ops.rmsnorm_conv(x, wn.reshape(-1).cuda().contiguous(), oh, oc, eps, conv_w=cw.t().contiguous().cuda(), state=store.state[0], b=b)
         r = 0
         for i, k in rows:
             got_h[i].append(oh[r:r + k].float().cpu())
@@ -188,6 +188,62 @@ def test_norm_and_causal_convolution_in_portions(D, taps, scalar, f32):
     o = torch.empty(lens[0], D, device="cuda", dtype=dt)
     seq_ops.rmsnorm_conv(xs[0].cuda().contiguous(), wn.reshape(-1).cuda().contiguous(), o, None, eps)
     assert worst_row(o.float(), ref_h[0]) < tol
+
+
+@pytest.mark.parametrize("D,taps,lens,plans", [(72, 4, [5000, 9, 2703], [[4000, 1, 2, 997], [1] * 9, [700, 2001, 2]]),
+                                               (1280, 3, [2500, 3, 1301], [[1, 2400, 99], [1, 1, 1], [1300, 1]]),
+                                               (250, 8, [3000, 5, 3000], [[2999, 1], [5], [3, 2997]])])
+@pytest.mark.parametrize("f32", [True, False])
+def test_norm_and_convolution_in_steps_of_thousands_of_rows(D, taps, lens, plans, f32):
+    """Long portions walk chunks of consecutive rows per CTA: chunk borders fall inside entries, on their first rows and on their last
+    ones; the entries' first rows and the state slots come from a launch of their own."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    from paligemma_multimodal_system_b200.cache import SequenceStore
+    g = torch.Generator().manual_seed(D)
+    eps = 1e-5
+    xs = [2.0 * torch.randn(n, D, generator=g) for n in lens]
+    wn, cw = torch.tensor([1.3]), torch.randn(D, taps, generator=g)
+    ref_h = [O.unit_rms(x, eps) * wn for x in xs]
+    ref_c = []
+    for h in ref_h:  # the convolution as shifted sums (the oracle's loop, vectorised over time)
+        acc = h.clone()
+        for j in range(taps):
+            s = taps - 1 - j
+            if s < h.shape[0]:
+                acc[s:] += cw[:, j] * h[:h.shape[0] - s]
+        ref_c.append(acc)
+    assert torch.allclose(ref_c[1], ref_h[1] + O.causal_conv(ref_h[1], cw), atol=1e-5)
+    store = SequenceStore([("state", (taps - 1, D))], max_tokens=sum(lens) + 256, num_slots=4, dtype=torch.float32)
+    store.state[0].fill_(1e4)
+    store.admit("unused")
+    for i in range(3):
+        store.admit(i)
+    dt = torch.float32 if f32 else torch.bfloat16
+    got_h, got_c = [[] for _ in lens], [[] for _ in lens]
+    fed, step = [0, 0, 0], 0
+    while any(fed[i] < lens[i] for i in range(3)):
+        es, rows = [], []
+        for i in range(3):
+            if fed[i] < lens[i] and step < len(plans[i]):
+                k = plans[i][step]
+                rec = store.reserve(i, k)
+                es.append(dict(tokens=[0] * k, ctx=rec.length, slot=rec.slot, pages=rec.pages))
+                rows.append((i, k))
+        b = seq_ops.make_step_batch(es)
+        x = torch.cat([xs[i][fed[i]:fed[i] + k] for i, k in rows]).cuda().contiguous()
+        oh, oc = torch.empty(b.T, D, device="cuda", dtype=dt), torch.empty(b.T, D, device="cuda", dtype=dt)
+        seq_ops.rmsnorm_conv(x, wn.cuda(), oh, oc, eps, conv_w=cw.t().contiguous().cuda(), state=store.state[0], b=b)
+        r = 0
+        for i, k in rows:
+            got_h[i].append(oh[r:r + k].float().cpu())
+            got_c[i].append(oc[r:r + k].float().cpu())
+            store.commit(i, k)
+            fed[i] += k
+            r += k
+        step += 1
+    tol = 1e-5 if f32 else 8e-3
+    for i in range(3):
+        assert worst_row(torch.cat(got_h[i]), ref_h[i]) < tol and worst_row(torch.cat(got_c[i]), ref_c[i]) < tol, i
 
 
 def test_convolution_state_survives_a_step_the_sequence_sits_out():
@@ -214,7 +270,7 @@ def test_convolution_state_survives_a_step_the_sequence_sits_out():
             xs.append((xa if i == 0 else xb)[rec.length:rec.length + k])
         b = seq_ops.make_step_batch(es)
         oc = torch.empty(b.T, D, device="cuda")
-        seq_ops.rmsnorm_conv(torch.cat(xs).cuda().contiguous(), wn.cuda(), None, oc, eps, conv_w=cw.cuda().contiguous(), state=store.state[0], b=b)
+        seq_ops.rmsnorm_conv(torch.cat(xs).cuda().contiguous(), wn.cuda(), None, oc, eps, conv_w=cw.t().contiguous().cuda(), state=store.state[0], b=b)
         r = 0
         for i, k in plan:
             got[i].append(oc[r:r + k].cpu())
