@@ -75,7 +75,7 @@ SIGNATURES = {
     "pg_attn_ragged_mma": [p, p, p, p, i64, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i32, p, p],
     "pg_attn_decode": [p, p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, i32, f32, f32, i32, i64, i64, i32, p, p],
     "pg_attn_decode_merge": [p, p, i64, p, p, p, i32, i32, i32, i32, i32, i32, p, p],
-    "pg_attn_latent_decode_mma": [p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, f32, p],
+    "pg_attn_latent_decode_mma": [p, p, p, i64, p, p, p, p, p, p, i32, i32, i32, i32, i32, i32, i32, f32, i32, p],
     "pg_linear_attn_scan": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_linear_attn_chunked": [p, i64, p, p, p, p, p, p, p, i32, i32, i32, i32, i32, p],
     "pg_gemm_simt_batched": [p, i64, i64, p, i64, i64, p, i64, i64, i32, i32, i32, i32, i32, i32, p],

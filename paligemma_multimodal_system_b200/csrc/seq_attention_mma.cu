@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
                                                                      const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                                      float* __restrict__ partial, const int* __restrict__ entry_row0,
                                                                      const int* __restrict__ entry_n, const int* __restrict__ entry_ctx,
-                                                                     const int* __restrict__ page_table, int max_pages, int page, int H, float scale) {
+                                                                     const int* __restrict__ page_table, int max_pages, int page, int H, float scale, int window) {
   constexpr int KS = DIM / 16, NV = VDIM / 8, LD = DIM + 8;
   static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && VDIM <= DIM && (KT == 32 || KT == 64), "tile shapes");
   constexpr int NB = KT / 8;  // 8-key blocks per tile
@@ -299,7 +299,8 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
   for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
   float m_l = -INFINITY, m_h = -INFINITY, l_l = 0.f, l_h = 0.f;
   const int* pt = page_table + (long long)e * max_pages;
-  const int ntiles = ctx / KT + 1;  // keys 0 .. ctx
+  const int lo = window > 0 ? max(0, ctx + 1 - window) : 0;  // a sliding window: keys lo .. ctx
+  const int tile0 = lo / KT, ntiles = ctx / KT + 1;           // tiles tile0 .. ntiles - 1 hold them
   const float sc2 = scale * 1.4426950408889634f;
   // lane's row address inside a 16-key x 16-column block for ldmatrix.x4.trans: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15)
   const int lm_key = (lane & 7) + ((lane >> 3) & 1) * 8, lm_col = (lane >> 4) * 8;
@@ -313,9 +314,9 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
     }
   };
   int cur = 0;
-  if (split < ntiles) fetch_tile(split, Kbuf);
+  if (tile0 + split < ntiles) fetch_tile(tile0 + split, Kbuf);
   asm volatile("cp.async.commit_group;" ::: "memory");
-  for (int it = split; it < ntiles; it += nsplit) {
+  for (int it = tile0 + split; it < ntiles; it += nsplit) {
     const int k0 = it * KT;
     const bf16* Ks = Kbuf + cur * KT * LD;
     if (it + nsplit < ntiles) fetch_tile(it + nsplit, Kbuf + (cur ^ 1) * KT * LD);  // that buffer was released by the barrier below
@@ -345,13 +346,13 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = k0 + nb * 8 + 2 * tq + (c & 1);
-        const float sc = key <= ctx ? sacc[nb][c] * sc2 : -INFINITY;
+        const float sc = (key <= ctx && key >= lo) ? sacc[nb][c] * sc2 : -INFINITY;
         sacc[nb][c] = sc;
         if (c & 2) mx_h = fmaxf(mx_h, sc); else mx_l = fmaxf(mx_l, sc);
       }
     mx_l = fmaxf(mx_l, __shfl_xor_sync(0xffffffffu, mx_l, 1)); mx_l = fmaxf(mx_l, __shfl_xor_sync(0xffffffffu, mx_l, 2));
     mx_h = fmaxf(mx_h, __shfl_xor_sync(0xffffffffu, mx_h, 1)); mx_h = fmaxf(mx_h, __shfl_xor_sync(0xffffffffu, mx_h, 2));
-    const float mn_l = fmaxf(m_l, mx_l), mn_h = fmaxf(m_h, mx_h);  // finite: key k0 <= ctx is visible to every row
+    const float mn_l = fmaxf(m_l, mx_l), mn_h = fmaxf(m_h, mx_h);  // finite: every tile of the loop holds a key in lo .. ctx, visible to every row
     const float corr_l = exp2f(m_l - mn_l), corr_h = exp2f(m_h - mn_h);
     float sum_l = 0.f, sum_h = 0.f;
 #pragma unroll
@@ -421,12 +422,12 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
 
 template <int DIM, int VDIM, int KT>
 int launch_latent_kt(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
-                     const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int warps, cudaStream_t st) {
+                     const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int window, int warps, cudaStream_t st) {
   const size_t smem = ((size_t)(16 * warps + 2 * KT) * (DIM + 8)) * sizeof(bf16);
   auto kern = attn_latent_decode_mma_kernel<DIM, VDIM, KT>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
   kern<<<dim3(nsplit, (H + 63) / 64, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),
-                                                                      ldg, static_cast<bf16*>(out), partial, row0, n, ctx, pt, max_pages, page, H, scale);
+                                                                      ldg, static_cast<bf16*>(out), partial, row0, n, ctx, pt, max_pages, page, H, scale, window);
   pg_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
@@ -434,11 +435,11 @@ int launch_latent_kt(const void* q, const void* pages, const void* gate, long lo
 // up to 32 heads = two warps per CTA: 32-key tiles keep four such CTAs on an SM (shared memory), 64-key tiles only two
 template <int DIM, int VDIM>
 int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
-                  const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, cudaStream_t st) {
+                  const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int window, cudaStream_t st) {
   const int warps = H >= 64 ? 4 : (H + 15) / 16;
   if (warps <= 2)
-    return launch_latent_kt<DIM, VDIM, 32>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, warps, st);
-  return launch_latent_kt<DIM, VDIM, 64>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, warps, st);
+    return launch_latent_kt<DIM, VDIM, 32>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
+  return launch_latent_kt<DIM, VDIM, 64>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
 }
 
 template <int DIM, int VDIM>
@@ -486,13 +487,14 @@ extern "C" int pg_attn_ragged_mma(const void* q, const void* k_pages, const void
 
 extern "C" int pg_attn_latent_decode_mma(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial,
                                          const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages,
-                                         int page, int entries, int nsplit, int H, int dim, int vdim, float scale, void* stream) {
+                                         int page, int entries, int nsplit, int H, int dim, int vdim, float scale, int window, void* stream) {
+  if (window < 0) return PG_ERR_ARG;
   if (entries <= 0 || entries > 65535 || nsplit <= 0 || nsplit > 64 || H <= 0 || page <= 0 || (nsplit > 1 && partial == nullptr)) return PG_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return PG_ERR_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define PG_LAT(D, V) \
   if (dim == D && vdim == V) \
-    return launch_latent<D, V>(q, pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, nsplit, H, scale, st)
+    return launch_latent<D, V>(q, pages, gate, ldg, out, partial, entry_row0, entry_n, entry_ctx, page_table, max_pages, page, entries, nsplit, H, scale, window, st)
   PG_LAT(96, 64);
   PG_LAT(160, 128);
   PG_LAT(192, 128);

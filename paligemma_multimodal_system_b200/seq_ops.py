@@ -321,6 +321,7 @@ class ScoreOptions:
         self.window = int(window) if window else 0
         self.keep_first = int(keep_first) if self.window else 0
         self._keep = (sink, dist_a, dist_b, head_scale)  # the struct holds raw pointers
+        self.window_only = sink is None and dist_a is None and head_scale is None and not self.keep_first  # nothing but a plain sliding window
         self.c = _lib.AttnScore(self.window, self.keep_first, _lib.ptr(sink), _lib.ptr(dist_a), _lib.ptr(dist_b), _lib.ptr(head_scale))
 
     def visible_keys(self, context):
@@ -367,14 +368,17 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
                    "pg_attn_ragged")
     latent = (k_pages.data_ptr() == v_pages.data_ptr() and G == 1 and krow == vrow == dim and k_pages.shape[-1] == dim)
     if (singles and not skip_singles and latent and tensor_cores and not f32 and (dim, vdim) in LATENT_MMA_SIZES and softcap in (0, 0.0, None)
-            and (gate is None or gph) and score is None):
+            and (gate is None or gph) and (score is None or score.window_only)):
         # one-row-per-token cache, every head of a token against the same key tile: tensor cores
+        window = score.window if score is not None else 0
         tiles = b.max_single_ctx // 64 + 1
+        if window:
+            tiles = min(tiles, (window + 62) // 64 + 1)  # a window of w keys touches at most this many 64-key tiles
         nsplit = max(1, min(tiles, (4 * _lib.num_sms()) // (singles * -(-H // 64)), 32))  # measured: 4 CTAs per SM beat 2 despite the larger merge
         partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
         _lib.check(L.pg_attn_latent_decode_mma(q.data_ptr(), k_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial), b.row0.data_ptr(),
                                                b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit, H, dim, vdim,
-                                               float(scale), _lib.stream()), "pg_attn_latent_decode_mma")
+                                               float(scale), int(window), _lib.stream()), "pg_attn_latent_decode_mma")
         if nsplit > 1:
             _lib.check(L.pg_attn_decode_merge(partial.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), b.row0.data_ptr(), b.n.data_ptr(), b.E, nsplit, H,
                                               vdim, gph, 0, 0, _lib.stream()), "pg_attn_decode_merge")

@@ -661,3 +661,44 @@ def test_wider_model_long_prompt_reaches_the_large_tile_paths():
     eng = engine_for(cfg, w, torch.bfloat16, max_tokens=1280, slots=2)
     poison(eng)
     assert close(run_cut(eng, "a", tk, [1100, 1]), ref, torch.bfloat16)
+
+
+@pytest.mark.parametrize("kv_rank,rot_dim,heads", [(64, 32, 8), (128, 32, 40), (256, 32, 32), (128, 64, 64)])
+@pytest.mark.parametrize("window", [1, 63, 64, 65, 200, 5000])
+def test_windowed_decode_of_cached_latent_rows_on_the_tensor_cores(kv_rank, rot_dim, heads, window):
+    """Row widths the tensor-core decode kernel of the absorbed form has, bf16: three sequences of unequal context decode together, the
+    window's first key at every place of a 64-key tile, a dominating key just inside and just outside the window."""
+    from paligemma_multimodal_system_b200 import seq_ops
+    from paligemma_multimodal_system_b200.cache import SequenceStore
+    kd, R, scale = kv_rank + rot_dim, kv_rank, 0.05
+    assert (kd, R) in seq_ops.LATENT_MMA_SIZES
+    ctxs = [700, 130, 5]
+    g = torch.Generator().manual_seed(window + kd)
+    store = SequenceStore([("latent", kd)], max_tokens=1024, num_slots=4, dtype=torch.bfloat16)
+    store.k_pages[0].fill_(1e4)
+    store.pool.take(1)
+    rows, qs, es = [], [], []
+    for i, c in enumerate(ctxs):
+        store.admit(i)
+        rec = store.reserve(i, c + 1)
+        keys = (0.5 * torch.randn(c + 1, kd, generator=g)).to(torch.bfloat16)
+        q = (0.5 * torch.randn(heads, kd, generator=g)).to(torch.bfloat16)
+        for needle in (c + 1 - window, c - window):  # the oldest key still seen, and the one before it
+            if needle >= 0:
+                keys[needle, 0] = 30.0 if needle == c + 1 - window else -30.0
+                keys[needle, 1:R] = 3.0 if needle == c + 1 - window else -3.0
+        q[:, 0] = 2.0
+        for j in range(c + 1):
+            store.k_pages[0][rec.pages[j // 64], j % 64] = keys[j].cuda()
+        rows.append(keys.double())
+        qs.append(q)
+        es.append(dict(tokens=[0], ctx=c, slot=rec.slot, pages=rec.pages))
+    b = seq_ops.make_step_batch(es)
+    out = torch.empty(3, heads * R, device="cuda", dtype=torch.bfloat16)
+    seq_ops.attn_ragged(torch.stack(qs).reshape(3, -1).cuda(), store.k_pages[0], store.k_pages[0], None, out, b, heads, 1, kd, R, scale, 0.0, 64, krow=kd, vrow=kd,
+                        gate_per_head=True, score=seq_ops.ScoreOptions(heads, window))
+    for i, c in enumerate(ctxs):
+        lo = max(0, c + 1 - window)
+        s = (qs[i].double() @ rows[i][lo:].T) * scale
+        ref = torch.softmax(s, -1) @ rows[i][lo:, :R]
+        assert worst_row(out[i].float().reshape(heads, R), ref) < 2e-2, (i, c)
