@@ -160,6 +160,115 @@ __global__ void __launch_bounds__(256) rmsnorm_conv_kernel(const float* __restri
   }
 }
 
+// The same scheme with four channels per thread and 16-byte accesses (D a multiple of 4, 16-byte aligned rows), and with every
+// register array indexed at compile time: the rows before an entry are held newest first (before[m] = h of the entry's row -1 - m),
+// so that row r's m-th earlier row is hf[r - 1 - m] or before[m - r] whatever taps is; taps beyond the real ones carry zero weights.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 mul4(float4 a, float s, float4 g) { return make_float4(a.x * s * g.x, a.y * s * g.y, a.z * s * g.z, a.w * s * g.w); }
+__device__ __forceinline__ void fma4(float4& acc, float4 a, float4 b) {
+  acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y); acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+}
+__device__ __forceinline__ void st_o4(float* p, long long i, float4 v) { *reinterpret_cast<float4*>(p + i) = v; }
+__device__ __forceinline__ void st_o4(bf16* p, long long i, float4 v) {
+  uint2 u;
+  u.x = pg::pack_bf16(v.x, v.y);
+  u.y = pg::pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(p + i) = u;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_conv_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, int w_stride,
+                                                               const float* __restrict__ cw, int taps, float* __restrict__ state,
+                                                               TO* __restrict__ out_h, TO* __restrict__ out_conv, const int* __restrict__ row_entry,
+                                                               const int* __restrict__ entry_row0, const int* __restrict__ entry_n,
+                                                               const int* __restrict__ entry_ctx, const int* __restrict__ entry_slot, int D, float eps,
+                                                               int by_entry) {
+  __shared__ float red[8];
+  __shared__ float inv[2 * MAX_K + 1];
+  const int K = cw != nullptr ? taps - 1 : 0;
+  const long long t = by_entry ? entry_row0[blockIdx.x] : blockIdx.x;
+  int i = 0, ne = 1, e = 0;
+  if (K > 0) {
+    e = by_entry ? (int)blockIdx.x : row_entry[t];
+    i = (int)(t - entry_row0[e]);
+    ne = entry_n[e];
+    if (i > 0 && i < K) return;
+  }
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (i >= K) {
+    if (by_entry) return;
+    for (int j = 0; j <= K; ++j) {
+      const float r = row_rstd(x + (t - K + j) * D, D, eps, red);
+      if (threadIdx.x == 0) inv[j] = r;
+    }
+    __syncthreads();
+    for (int c = 4 * threadIdx.x; c < D; c += 1024) {
+      float4 g;
+      if (w_stride) g = ld4(w + c);
+      else g.x = g.y = g.z = g.w = w[0];
+      float4 acc = zero, hv = zero;
+#pragma unroll
+      for (int j = 0; j <= MAX_K; ++j) {
+        if (j <= K) {
+          const float4 hj = mul4(ld4(x + (t - K + j) * D + c), inv[j], g);
+          if (cw != nullptr) fma4(acc, ld4(cw + (long long)j * D + c), hj);
+          if (j == K) hv = hj;
+        }
+      }
+      if (out_h != nullptr) st_o4(out_h, t * D + c, hv);
+      if (out_conv != nullptr) st_o4(out_conv, t * D + c, make_float4(hv.x + acc.x, hv.y + acc.y, hv.z + acc.z, hv.w + acc.w));
+    }
+    return;
+  }
+  // i == 0 < K: the entry's first m rows and the slot
+  const int m = min(ne, K);
+  for (int r = 0; r < m; ++r) {
+    const float a = row_rstd(x + (t + r) * D, D, eps, red);
+    if (threadIdx.x == 0) inv[r] = a;
+  }
+  for (int mm = 0; mm < m; ++mm) {  // the entry's last rows, newest first
+    const int row = ne - 1 - mm;
+    const float b = row < m ? 0.f : row_rstd(x + (t + row) * D, D, eps, red);
+    if (threadIdx.x == 0 && row >= m) inv[MAX_K + mm] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x < m && ne - 1 - (int)threadIdx.x < m) inv[MAX_K + threadIdx.x] = inv[ne - 1 - threadIdx.x];
+  __syncthreads();
+  const bool fresh = entry_ctx[e] == 0;  // nothing before this entry: zeros, whatever an earlier sequence left in the slot
+  float* slot = state + (long long)entry_slot[e] * K * D;
+  for (int c = 4 * threadIdx.x; c < D; c += 1024) {
+    float4 g;
+    if (w_stride) g = ld4(w + c);
+    else g.x = g.y = g.z = g.w = w[0];
+    float4 before[MAX_K], cwr[MAX_K], hf[MAX_K];
+    const float4 cwcur = ld4(cw + (long long)K * D + c);
+#pragma unroll
+    for (int mm = 0; mm < MAX_K; ++mm) {
+      before[mm] = (mm < K && !fresh) ? ld4(slot + (long long)(K - 1 - mm) * D + c) : zero;
+      cwr[mm] = mm < K ? ld4(cw + (long long)(K - 1 - mm) * D + c) : zero;
+      hf[mm] = mm < m ? mul4(ld4(x + (t + mm) * D + c), inv[mm], g) : zero;
+    }
+#pragma unroll
+    for (int r = 0; r < MAX_K; ++r) {
+      if (r < m) {
+        float4 acc = zero;
+        fma4(acc, cwcur, hf[r]);
+#pragma unroll
+        for (int mm = 0; mm < MAX_K; ++mm) fma4(acc, cwr[mm], mm < r ? hf[r - 1 - mm] : before[mm - r]);
+        if (out_h != nullptr) st_o4(out_h, (t + r) * D + c, hf[r]);
+        if (out_conv != nullptr) st_o4(out_conv, (t + r) * D + c, make_float4(hf[r].x + acc.x, hf[r].y + acc.y, hf[r].z + acc.z, hf[r].w + acc.w));
+      }
+    }
+    // the slot afterwards, oldest first: rows of before the entry move up by ne, the entry's last rows follow
+#pragma unroll
+    for (int mm = 0; mm < MAX_K; ++mm)
+      if (mm < K && mm + ne < K) *reinterpret_cast<float4*>(slot + (long long)(K - 1 - mm - ne) * D + c) = before[mm];
+#pragma unroll
+    for (int mm = 0; mm < MAX_K; ++mm)
+      if (mm < m) *reinterpret_cast<float4*>(slot + (long long)(K - 1 - mm) * D + c) = mul4(ld4(x + (t + ne - 1 - mm) * D + c), inv[MAX_K + mm], g);
+  }
+}
+
 // Prompt portions: one CTA per chunk of RC consecutive rows.  Pass 1: a warp per row (the chunk and the taps - 1 rows before it) leaves
 // 1 / rms in shared memory.  Pass 2: a thread owns four channels and walks down the chunk's rows; the earlier rows it needs are the
 // ones it read in its last iterations (L1).  Rows less than taps - 1 tokens
@@ -319,26 +428,31 @@ extern "C" int pg_rmsnorm_conv(const float* x, const float* w, int w_scalar, con
   // prompt portions: chunks of consecutive rows, about two waves of four CTAs per SM; the entries' first rows and slots in a launch of their own
   const int RC = min(32, (rows + 8 * pg::num_sms() - 1) / (8 * pg::num_sms()));
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (conv_w != nullptr && taps > 1 && entries > 0 && RC >= 2 && D % 4 == 0 && al16(x) && al16(w) && al16(conv_w) && al16(out_h) && al16(out_conv)) {
+  if (conv_w != nullptr && taps > 1 && entries > 0 && RC >= 2 && D % 4 == 0 && al16(x) && (w_scalar || al16(w)) && al16(conv_w) && al16(state) && al16(out_h) && al16(out_conv)) {
     const int chunks = (rows + RC - 1) / RC;
     if (out_f32) {
       rmsnorm_conv_rows_kernel<float><<<chunks, 256, 0, st>>>(x, w, ws, conv_w, taps, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry, entry_row0, rows, RC, D, eps);
-      rmsnorm_conv_kernel<float><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry,
-                                                          entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
+      rmsnorm_conv_vec_kernel<float><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry,
+                                                              entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
     } else {
       rmsnorm_conv_rows_kernel<bf16><<<chunks, 256, 0, st>>>(x, w, ws, conv_w, taps, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry, entry_row0, rows, RC, D, eps);
-      rmsnorm_conv_kernel<bf16><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry,
-                                                         entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
+      rmsnorm_conv_vec_kernel<bf16><<<entries, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry,
+                                                             entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 1);
     }
     pg_count_launch(1);
     PG_RET();
   }
-  if (out_f32)
-    rmsnorm_conv_kernel<float><<<rows, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<float*>(out_h), static_cast<float*>(out_conv), row_entry,
-                                                     entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 0);
-  else
-    rmsnorm_conv_kernel<bf16><<<rows, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<bf16*>(out_h), static_cast<bf16*>(out_conv), row_entry,
-                                                    entry_row0, entry_n, entry_ctx, entry_slot, D, eps, 0);
+  const bool vec = D % 4 == 0 && al16(x) && (w_scalar || al16(w)) && al16(conv_w) && al16(state) && al16(out_h) && al16(out_conv);
+#define PG_RC(KERN, TO, GRID, BY)                                                                                                                     \
+  KERN<TO><<<GRID, 256, 0, st>>>(x, w, ws, conv_w, taps, state, static_cast<TO*>(out_h), static_cast<TO*>(out_conv), row_entry, entry_row0, entry_n, \
+                                 entry_ctx, entry_slot, D, eps, BY)
+  if (vec) {
+    if (out_f32) PG_RC(rmsnorm_conv_vec_kernel, float, rows, 0);
+    else PG_RC(rmsnorm_conv_vec_kernel, bf16, rows, 0);
+  } else {
+    if (out_f32) PG_RC(rmsnorm_conv_kernel, float, rows, 0);
+    else PG_RC(rmsnorm_conv_kernel, bf16, rows, 0);
+  }
   PG_RET();
 }
 
