@@ -728,6 +728,13 @@ def run_zigivik(args):
     model = random_zigivik(cfg)
     eng = _throughput(model, args, flush, V, "zigivik", out)
     prec, k, store = model.prec, {}, eng.store
+    # the like kernel of the latent mixer: the same class as Pukerax uses it (no window, one gate per head, interleaved rotation), equal sizes
+    from .mixers import LatentAttention
+    lm = cfg["layers"][0]["mixer"]
+    plain = LatentAttention(W, H, lm["dim"], lm["rot_dim"], lm["vdim"], lm["q_rank"], lm["kv_rank"], lm["scale"], lm["rot_dim"], 1e6, 1e-6)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    plain.load(lambda name, shape: (torch.randn(tuple(shape), device="cuda", generator=gen) * shape[-1] ** -0.5 + (1.0 if len(shape) == 1 else 0.0)).to(torch.bfloat16), "")
+    plain.pack(prec)
     for name, (n_seq, n_new, c0) in {"prefill": (B_pre, S, 0), "decode": (B_dec, 1, ctx)}.items():
         b = _entries(store, n_seq, n_new, c0)
         T = b.T
@@ -763,6 +770,11 @@ def run_zigivik(args):
                 fl = 2 * T * W * mx.w_in.shape[0] + 2 * T * H * dh * W + 4 * dh * H * pairs
                 by = wts + n_seq * (c0 + n_new) * G * 2 * dh * 2 + T * W * (2 + 8)
             k[f"mixer_{tag}_{name}"] = dict(s=timed(lambda: mx(hin, b, store, li, prec, resid=x, resid_scale=0.5), flush=flush), flops=fl, bytes=by)
+            if li == 0:  # the plain latent mixer over the same pages: every key is visible
+                allp = n_seq * sum(i + 1 for i in range(c0, c0 + n_new))
+                fl_p = fl + ((4 * H * (dh + mx.rot // 2) * (allp - pairs)) if n_new > 1 else (2 * H * (kd + R) * (allp - pairs)))
+                k[f"pukerax_form_latent_mixer_{name}"] = dict(s=timed(lambda: plain(hin, b, store, 0, prec, resid=x), flush=flush), flops=fl_p,
+                                                              bytes=by + n_seq * max(0, c0 + n_new - min(c0 + n_new, win + n_new)) * kd * 2)
         for i in range(n_seq):
             store.release(("k", i))
     del eng, model, store
