@@ -419,7 +419,7 @@ int pg_attn_decode_merge(const float* partial, const void* gate, long long ldg, 
  * tile (mma.sync, fp32 probabilities as three bf16 terms, values read from the key tile with ldmatrix.trans).  gate: one scalar
  * per head (gate[t * ldg + h]) or NULL.  nsplit > 1: partial triples in the layout above, to be finished by pg_attn_decode_merge.
  * window > 0: a token at position i reads keys i - window + 1 .. i only (0: all keys).
- * (dim, vdim) in {(96,64), (160,128), (192,128), (288,256)}; anything else returns PG_ERR_ARG and belongs to pg_attn_decode. */
+ * (dim, vdim) in {(96,64), (160,128), (192,128), (288,256), (544,512), (576,512)}; anything else returns PG_ERR_ARG and belongs to pg_attn_decode. */
 int pg_attn_latent_decode_mma(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial,
                               const int* entry_row0, const int* entry_n, const int* entry_ctx, const int* page_table, int max_pages,
                               int page, int entries, int nsplit, int H, int dim, int vdim, float scale, int window, void* stream);

@@ -267,18 +267,19 @@ __global__ void __launch_bounds__(128, (DIM + VDIM <= 128) ? 4 : 2) attn_ragged_
 // P V takes its B operand from the SAME tile with ldmatrix.trans (key-major rows -> the k-pairs an m16n8k16 B fragment wants),
 // so the values are neither stored nor fetched separately; probabilities stay fp32 and enter as three bf16 terms.
 // With several key splits the (max, sum, accumulator) triples go to `partial` in the layout of pg_attn_decode and its merge
-// kernel finishes the rows.
+// kernel finishes the rows.  VS > 1: the value columns are shared out over VS CTAs (each recomputes the scores; a thread's accumulators
+// stay at 128 registers for value parts up to 512 wide).
 // ---------------------------------------------------------------------------------------------------------------------
-template <int DIM, int VDIM, int KT>
+template <int DIM, int VDIM, int KT, int VS>
 __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pages,
                                                                      const bf16* __restrict__ gate, long long ldg, bf16* __restrict__ out,
                                                                      float* __restrict__ partial, const int* __restrict__ entry_row0,
                                                                      const int* __restrict__ entry_n, const int* __restrict__ entry_ctx,
                                                                      const int* __restrict__ page_table, int max_pages, int page, int H, float scale, int window) {
-  constexpr int KS = DIM / 16, NV = VDIM / 8, LD = DIM + 8;
-  static_assert(DIM % 16 == 0 && VDIM % 16 == 0 && VDIM <= DIM && (KT == 32 || KT == 64), "tile shapes");
+  constexpr int VPART = VDIM / VS, KS = DIM / 16, NV = VPART / 8, LD = DIM + 8;
+  static_assert(DIM % 16 == 0 && VDIM % VS == 0 && VPART % 16 == 0 && VDIM <= DIM && (KT == 32 || KT == 64), "tile shapes");
   constexpr int NB = KT / 8;  // 8-key blocks per tile
-  const int e = blockIdx.z, h0 = blockIdx.y * 64, split = blockIdx.x, nsplit = gridDim.x;
+  const int e = blockIdx.z, h0 = (blockIdx.y / VS) * 64, v0 = (blockIdx.y % VS) * VPART, split = blockIdx.x, nsplit = gridDim.x;
   if (entry_n[e] != 1) return;
   const int ctx = entry_ctx[e];
   const long long t = entry_row0[e];
@@ -378,7 +379,7 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
       split3(sacc[2 * kk][2], sacc[2 * kk][3], a1[1], a2[1], a3[1]);
       split3(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], a1[2], a2[2], a3[2]);
       split3(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], a1[3], a2[3], a3[3]);
-      const bf16* vbase = Ks + (kk * 16 + lm_key) * LD + lm_col;
+      const bf16* vbase = Ks + (kk * 16 + lm_key) * LD + lm_col + v0;
 #pragma unroll
       for (int np = 0; np < NV / 2; ++np) {
         uint32_t b0, b1, b2, b3;
@@ -406,40 +407,42 @@ __global__ void __launch_bounds__(128) attn_latent_decode_mma_kernel(const bf16*
       if (gate != nullptr) g *= 1.0f / (1.0f + expf(-__bfloat162float(gate[t * ldg + head])));
 #pragma unroll
       for (int nv = 0; nv < NV; ++nv)
-        *reinterpret_cast<__nv_bfloat162*>(out + (t * H + head) * VDIM + nv * 8 + 2 * tq) =
+        *reinterpret_cast<__nv_bfloat162*>(out + (t * H + head) * VDIM + v0 + nv * 8 + 2 * tq) =
             __floats2bfloat162_rn(oacc[nv][2 * half] * g, oacc[nv][2 * half + 1] * g);
     } else {
       float* pp = partial + (((long long)e * H + head) * nsplit + split) * (VDIM + 2);
-      if (tq == 0) { pp[0] = mrow * 0.6931471805599453f; pp[1] = lsum; }  // the merge kernel works with natural exponentials
+      if (tq == 0 && v0 == 0) { pp[0] = mrow * 0.6931471805599453f; pp[1] = lsum; }  // the merge kernel works with natural exponentials
 #pragma unroll
       for (int nv = 0; nv < NV; ++nv) {
-        pp[2 + nv * 8 + 2 * tq] = oacc[nv][2 * half];
-        pp[2 + nv * 8 + 2 * tq + 1] = oacc[nv][2 * half + 1];
+        pp[2 + v0 + nv * 8 + 2 * tq] = oacc[nv][2 * half];
+        pp[2 + v0 + nv * 8 + 2 * tq + 1] = oacc[nv][2 * half + 1];
       }
     }
   }
 }
 
-template <int DIM, int VDIM, int KT>
+template <int DIM, int VDIM, int KT, int VS>
 int launch_latent_kt(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
                      const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int window, int warps, cudaStream_t st) {
   const size_t smem = ((size_t)(16 * warps + 2 * KT) * (DIM + 8)) * sizeof(bf16);
-  auto kern = attn_latent_decode_mma_kernel<DIM, VDIM, KT>;
+  auto kern = attn_latent_decode_mma_kernel<DIM, VDIM, KT, VS>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return PG_ERR_CUDA;
-  kern<<<dim3(nsplit, (H + 63) / 64, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),
+  kern<<<dim3(nsplit, ((H + 63) / 64) * VS, entries), 32 * warps, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(pages), static_cast<const bf16*>(gate),
                                                                       ldg, static_cast<bf16*>(out), partial, row0, n, ctx, pt, max_pages, page, H, scale, window);
   pg_count_launch(1);
   return cudaGetLastError() == cudaSuccess ? PG_OK : PG_ERR_CUDA;
 }
 
-// up to 32 heads = two warps per CTA: 32-key tiles keep four such CTAs on an SM (shared memory), 64-key tiles only two
+// up to 32 heads = two warps per CTA: 32-key tiles keep four such CTAs on an SM (shared memory), 64-key tiles only two; rows wider than
+// 288 always take 32-key tiles (shared memory) and two CTAs per value half
 template <int DIM, int VDIM>
 int launch_latent(const void* q, const void* pages, const void* gate, long long ldg, void* out, float* partial, const int* row0, const int* n,
                   const int* ctx, const int* pt, int max_pages, int page, int entries, int nsplit, int H, float scale, int window, cudaStream_t st) {
   const int warps = H >= 64 ? 4 : (H + 15) / 16;
-  if (warps <= 2)
-    return launch_latent_kt<DIM, VDIM, 32>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
-  return launch_latent_kt<DIM, VDIM, 64>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
+  constexpr int VS = VDIM > 256 ? 2 : 1;
+  if (warps <= 2 || DIM > 288)
+    return launch_latent_kt<DIM, VDIM, 32, VS>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
+  return launch_latent_kt<DIM, VDIM, 64, VS>(q, pages, gate, ldg, out, partial, row0, n, ctx, pt, max_pages, page, entries, nsplit, H, scale, window, warps, st);
 }
 
 template <int DIM, int VDIM>
@@ -499,6 +502,8 @@ extern "C" int pg_attn_latent_decode_mma(const void* q, const void* pages, const
   PG_LAT(160, 128);
   PG_LAT(192, 128);
   PG_LAT(288, 256);
+  PG_LAT(544, 512);
+  PG_LAT(576, 512);
 #undef PG_LAT
   return PG_ERR_ARG;  // other row sizes: pg_attn_decode
 }

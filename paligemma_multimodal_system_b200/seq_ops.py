@@ -334,7 +334,7 @@ MMA_HEAD_SIZES = {(32, 32), (64, 64), (128, 128), (64, 128), (128, 64), (96, 64)
 
 
 # (row width, value width) of a one-row-per-token cache the tensor-core decode kernel is instantiated for
-LATENT_MMA_SIZES = {(96, 64), (160, 128), (192, 128), (288, 256)}
+LATENT_MMA_SIZES = {(96, 64), (160, 128), (192, 128), (288, 256), (544, 512), (576, 512)}
 
 
 def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, scale, softcap, page, decode_kernel=True, tensor_cores=True,
@@ -374,7 +374,8 @@ def attn_ragged(q, k_pages, v_pages, gate, out, b: StepBatch, H, G, dim, vdim, s
         tiles = b.max_single_ctx // 64 + 1
         if window:
             tiles = min(tiles, (window + 62) // 64 + 1)  # a window of w keys touches at most this many 64-key tiles
-        nsplit = max(1, min(tiles, (4 * _lib.num_sms()) // (singles * -(-H // 64)), 32))  # measured: 4 CTAs per SM beat 2 despite the larger merge
+        vs = 2 if vdim > 256 else 1  # value halves are CTAs of their own
+        nsplit = max(1, min(tiles, (4 * _lib.num_sms()) // (singles * -(-H // 64) * vs), 32))  # measured: 4 CTAs per SM beat 2 despite the larger merge
         partial = torch.empty(b.E * H * nsplit * (vdim + 2), device="cuda", dtype=torch.float32) if nsplit > 1 else None
         _lib.check(L.pg_attn_latent_decode_mma(q.data_ptr(), k_pages.data_ptr(), _lib.ptr(gate), ldg, out.data_ptr(), _lib.ptr(partial), b.row0.data_ptr(),
                                                b.n.data_ptr(), b.ctx.data_ptr(), b.page_table.data_ptr(), b.max_pages, page, b.E, nsplit, H, dim, vdim,

@@ -663,7 +663,7 @@ def test_wider_model_long_prompt_reaches_the_large_tile_paths():
     assert close(run_cut(eng, "a", tk, [1100, 1]), ref, torch.bfloat16)
 
 
-@pytest.mark.parametrize("kv_rank,rot_dim,heads", [(64, 32, 8), (128, 32, 40), (256, 32, 32), (128, 64, 64)])
+@pytest.mark.parametrize("kv_rank,rot_dim,heads", [(64, 32, 8), (128, 32, 40), (256, 32, 32), (128, 64, 64), (512, 32, 32), (512, 64, 72)])
 @pytest.mark.parametrize("window", [1, 63, 64, 65, 200, 5000])
 def test_windowed_decode_of_cached_latent_rows_on_the_tensor_cores(kv_rank, rot_dim, heads, window):
     """Row widths the tensor-core decode kernel of the absorbed form has, bf16: three sequences of unequal context decode together, the
