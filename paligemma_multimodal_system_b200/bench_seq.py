@@ -662,8 +662,8 @@ def zigivik_config(width, heads, kv_heads, dim, ff, vocab, layers, taps=4):
     grouped attention whose keys are the values, and a latent layer that borrows the first one's cached rows (window 512).  At width 2048 a
     cached latent row is 256 + 32 wide, a size the tensor-core decode kernel of the absorbed form is built for."""
     lat = {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": width // 2, "kv_rank": width // 8, "scale": (dim + dim // 2) ** -0.5,
-           "rot": {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
-    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 2.5e5, "dims": dim}}
+           "rot": {"base": 5e5, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 1.0}}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 1e5, "dims": dim}}
     ls = []
     for i in range(layers):
         k = i % 4

@@ -37,7 +37,7 @@ def with_ff(l, ff=80):
     return dict(l, mlp={"kind": "dense", "ff": ff} if ff else None)
 
 
-def make_cfg(layers, width=72, vocab=90, eps=1e-5, taps=3, mult=0.6):
+def make_cfg(layers, width=72, vocab=90, eps=1e-5, taps=4, mult=0.6):
     return {"architecture": "Zigivik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "canon": {"taps": taps}, "residual_mult": mult, "layers": layers}
 
 
