@@ -702,3 +702,45 @@ def test_windowed_decode_of_cached_latent_rows_on_the_tensor_cores(kv_rank, rot_
         s = (qs[i].double() @ rows[i][lo:].T) * scale
         ref = torch.softmax(s, -1) @ rows[i][lo:, :R]
         assert worst_row(out[i].float().reshape(heads, R), ref) < 2e-2, (i, c)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_runner_replays_a_mixed_schedule(tmp_path, dtype):
+    """bin/trace_run on a checkpoint folder: portions beside single tokens, a step that wants nothing, a request that sits out a step,
+    a finished request's page and slot taken over by a later one; the written logits equal the oracle's for each request alone."""
+    import subprocess
+    import numpy as np
+    cfg = OTHER_SIZES[0]
+    w = O.random_weights(cfg, seed=13)
+    meta, blobs, off = {}, [], 0
+    for name, t in w.items():
+        raw = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        meta[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    head = json.dumps(meta).encode()
+    (tmp_path / "model").mkdir()
+    (tmp_path / "model" / "model.safetensors").write_bytes(struct.pack("<Q", len(head)) + head + b"".join(blobs))
+    (tmp_path / "model" / "config.json").write_text(json.dumps(cfg))
+    V = cfg["vocab"]
+    tk = {"a": toks(70, V, 1), "b": toks(33, V, 2), "c": toks(1, V, 3), "d": toks(20, V, 4)}
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": tk["a"][:40], "want": [0, 39]}, {"id": "b", "tokens": tk["b"][:2], "want": [1]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": tk["a"][40:41], "want": [0]}, {"id": "c", "tokens": tk["c"], "want": [0]}], "end": ["c"]},
+        {"step": 2, "entries": [{"id": "b", "tokens": tk["b"][2:32], "want": []}, {"id": "a", "tokens": tk["a"][41:42], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "d", "tokens": tk["d"][:19], "want": [18]}, {"id": "a", "tokens": tk["a"][42:], "want": [27]}, {"id": "b", "tokens": tk["b"][32:], "want": [0]}],
+         "end": ["a", "b"]},
+        {"step": 4, "entries": [{"id": "d", "tokens": tk["d"][19:], "want": [0]}], "end": ["d"]},
+    ]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(tmp_path / "model"), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "256"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    assert not (out / "2.f32").exists()
+    ref = {k: O.forward(cfg, w, v) for k, v in tk.items()}
+    want = {0: [("a", 0), ("a", 39), ("b", 1)], 1: [("a", 40), ("c", 0)], 3: [("d", 18), ("a", 69), ("b", 32)], 4: [("d", 19)]}
+    dt = torch.float32 if dtype == "float32" else torch.bfloat16
+    for step, rows in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), V).copy())
+        assert close(got, torch.stack([ref[k][p] for k, p in rows]), dt), step
